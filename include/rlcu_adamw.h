@@ -1,0 +1,212 @@
+/*
+ * rlcu_adamw.h -- C ABI of the B200 (sm_100a) optimizer step for RL.cu.
+ *
+ * Scope: the mixed-precision fused AdamW update and the gradient unscale /
+ * non-finite check / global L2 norm / clip around it, i.e. what RL.cu runs at
+ * the end of every SFT and GRPO optimizer step.  Each entry point names the
+ * RL.cu interface it stands in for (paths inside the RL.cu tree).
+ *
+ * Conventions
+ *   - Every function returns an int status (RLCU_OK == 0).  Nothing here exits
+ *     the process, throws, or synchronises the device unless it says so.
+ *   - All data pointers are DEVICE pointers on the current device unless a
+ *     parameter is documented as a host pointer.  Buffers are owned by the
+ *     caller and must not alias each other.
+ *   - `stream` is a cudaStream_t passed as void* so that this header needs no
+ *     CUDA headers; NULL is the legacy default stream, which is what RL.cu uses.
+ *   - FP16 data is IEEE binary16 (`__half`), passed as void*.
+ *   - Sizes are 64-bit element counts.  RL.cu's `int n` launchers are kept
+ *     separately in include/kernels/adamw.cuh for source compatibility.
+ *   - There is no CPU fallback: without a CUDA device every compute entry
+ *     point fails with RLCU_ERR_CUDA.
+ */
+#ifndef RLCU_ADAMW_H
+#define RLCU_ADAMW_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RLCU_ABI_VERSION 1
+
+/* status codes */
+enum {
+    RLCU_OK = 0,
+    RLCU_ERR_INVALID = 1,   /* bad argument (null, size, alignment, kind)      */
+    RLCU_ERR_CUDA = 2,      /* a CUDA runtime call failed                      */
+    RLCU_ERR_NCCL = 3,      /* an NCCL call failed                             */
+    RLCU_ERR_TIMEOUT = 4,   /* a bounded device-side wait gave up              */
+    RLCU_ERR_UNSUPPORTED = 5
+};
+
+/* element kinds */
+enum { RLCU_F16 = 0, RLCU_F32 = 1 };
+
+/* per-tensor flags */
+enum {
+    RLCU_TENSOR_NORM_ONLY = 1u, /* counted in the gradient norm, never updated.
+                                   RL.cu's clip covers the whole FP32 gradient pool,
+                                   which ends with an attention workspace that is not
+                                   a parameter (trainer.h:331, qwen3.cu:1038-1042).   */
+    RLCU_TENSOR_GRAD_ZERO = 2u  /* gradient is taken as zero without being read:
+                                   RL.cu's freeze_embed memset (trainer.h:271-277).   */
+};
+
+/* flags of the update pass */
+enum {
+    RLCU_STEP_ROUND_CLIP_FP16 = 1u, /* when the clip is active, round g*coef to FP16
+                                       before use, as RL.cu's scale_half_kernel
+                                       stores it (trainer.h:136-139). FP16 tensors only. */
+    RLCU_STEP_DEVICE_BIAS_CORRECTION = 2u, /* take 1-beta^t from the statistics record
+                                       (written by the statistics pass when a device-side
+                                       scaler state is attached) instead of rlcu_hparams */
+    RLCU_STEP_ZERO_GRADS = 4u       /* write zeros over each gradient after reading it:
+                                       folds RL.cu's qwen3_gradients_zero (qwen3.cu:1109-1112)
+                                       into the update                                   */
+};
+
+/* flags of the statistics pass */
+enum {
+    RLCU_STAT_PARTIAL = 1u  /* only write sum_sq (this rank's share); the caller
+                               all-reduces it and calls rlcu_gradstat_finalize        */
+};
+
+/* One parameter tensor.  Mirrors one slice of RL.cu's flat pools: param/grad
+ * from Qwen3Weights / Qwen3Gradients (weights.h:43-61, qwen3.h:190-218), m / v /
+ * master from AdamWOptimizer's state (optimizer.h:150-156). 64 bytes. */
+typedef struct rlcu_tensor_desc {
+    void*       param;        /* __half* or float* by dtype; updated in place         */
+    const void* grad;         /* same kind as param; may be NULL with GRAD_ZERO        */
+    float*      m;            /* first moment                                          */
+    float*      v;            /* second moment                                         */
+    float*      master;       /* FP32 master copy (F16 only) or NULL.  With a master,
+                                 param is write-only, as in launch_adamw_fp16.         */
+    uint64_t    n;            /* elements                                              */
+    float       weight_decay; /* decoupled; RL.cu uses 0 for embedding and norms
+                                 (optimizer.h:131-146)                                 */
+    uint32_t    dtype;        /* RLCU_F16 / RLCU_F32                                   */
+    uint32_t    flags;        /* RLCU_TENSOR_*                                         */
+    uint32_t    reserved;     /* must be 0                                             */
+} rlcu_tensor_desc;
+
+/* Step hyper-parameters: AdamWOptimizer's public fields (optimizer.h:62-66) and
+ * the two bias corrections it computes per step (optimizer.h:121-122). */
+typedef struct rlcu_hparams {
+    float lr, beta1, beta2, eps;
+    float bias_correction1;   /* 1 - beta1^t (NOT the inverse, adamw.cuh:36-37)        */
+    float bias_correction2;   /* 1 - beta2^t                                            */
+} rlcu_hparams;
+
+/* Statistics record in device memory, produced by the statistics pass and read
+ * by the update pass without a host round trip (RL.cu reads the sum back to the
+ * host in the middle of the step, trainer.h:340). 64 bytes, 16-byte aligned. */
+typedef struct rlcu_stat {
+    double   sum_sq;       /* sum over all listed gradients of (g*unscale)^2            */
+    float    norm;         /* sqrtf((float)sum_sq): the PRE-clip norm RL.cu logs        */
+    float    coef;         /* what each gradient is multiplied by: unscale, times
+                              max_norm/(norm+1e-6) when norm > max_norm (trainer.h:343-344) */
+    uint32_t found_inf;    /* 1: some gradient is inf/NaN -> the update writes nothing  */
+    uint32_t clip_active;  /* 1: norm > max_norm                                        */
+    float    bias_correction1; /* valid when a scaler state was attached                */
+    float    bias_correction2;
+    int32_t  step;         /* Adam step t the update pass belongs to (scaler attached)  */
+    float    loss_scale;   /* scale the gradients of THIS step carried                  */
+    uint32_t reserved[6];
+} rlcu_stat;
+
+/* Dynamic loss-scale and step-counter state in device memory.  No counterpart
+ * in RL.cu (it has no loss scaling): halve on overflow, double after
+ * growth_interval consecutive clean steps; an overflowed step is skipped and
+ * does not advance the Adam step counter. 32 bytes. */
+typedef struct rlcu_scaler_state {
+    float   scale;
+    int32_t growth_tracker;
+    int32_t step;             /* Adam step counter t (clean steps so far)              */
+    int32_t skipped;          /* overflowed steps so far                               */
+    int32_t growth_interval;
+    float   beta1, beta2;     /* for the device-side 1-beta^t                          */
+    float   grad_mul;         /* extra factor folded into unscale (1/world after a
+                                 summed reduce-scatter); 0 is read as 1                */
+} rlcu_scaler_state;
+
+typedef struct rlcu_tensor_list rlcu_tensor_list;
+
+/* -------- library ------------------------------------------------------ */
+int         rlcu_abi_version(void);
+/* message of the last failure on the calling thread (never NULL) */
+const char* rlcu_last_error(void);
+
+/* -------- single tensor: RL.cu's launchers ----------------------------- */
+/* launch_adamw_fp16 (include/kernels/adamw.cuh:24-39, src/kernels/adamw.cu:42-58):
+ * FP32 master/m/v updated in place, FP16 model weight written, FP16 grad read.
+ * n <= 0 is a silent no-op as in adamw.cu:49. */
+int rlcu_adamw_fp16_master(float* master_w, void* model_w, const void* grad, float* m, float* v,
+                           int64_t n, float lr, float beta1, float beta2, float eps,
+                           float weight_decay, float bias_correction1, float bias_correction2,
+                           void* stream);
+/* Same arithmetic without a master copy: the weight is read from the FP16
+ * parameter (12 bytes read + 10 written per element).  No RL.cu counterpart. */
+int rlcu_adamw_fp16(void* param, const void* grad, float* m, float* v,
+                    int64_t n, float lr, float beta1, float beta2, float eps,
+                    float weight_decay, float bias_correction1, float bias_correction2,
+                    void* stream);
+/* launch_adamw_fp32 (include/kernels/adamw.cuh:43-57, src/kernels/adamw.cu:93-108) */
+int rlcu_adamw_fp32(float* w, const float* grad, float* m, float* v,
+                    int64_t n, float lr, float beta1, float beta2, float eps,
+                    float weight_decay, float bias_correction1, float bias_correction2,
+                    void* stream);
+/* fp16_to_fp32 master initialisation (include/training/optimizer.h:46-57) */
+int rlcu_half_to_float(float* dst, const void* src, int64_t n, void* stream);
+
+/* -------- tensor list --------------------------------------------------- */
+/* Builds the device-side work table for `count` tensors (host array `descs`).
+ * Allocates device memory (table + reduction scratch) on the current device and
+ * copies synchronously; call it at set-up, like AdamWOptimizer::init
+ * (optimizer.h:188-250).  Tensors with n == 0 are allowed and ignored. */
+int rlcu_tensor_list_create(const rlcu_tensor_desc* descs, uint64_t count, rlcu_tensor_list** out);
+int rlcu_tensor_list_destroy(rlcu_tensor_list* list);
+/* elements the update pass touches / elements the statistics pass reads */
+uint64_t rlcu_tensor_list_numel(const rlcu_tensor_list* list);
+uint64_t rlcu_tensor_list_stat_numel(const rlcu_tensor_list* list);
+uint64_t rlcu_tensor_list_work_items(const rlcu_tensor_list* list);
+
+/* -------- statistics pass: Trainer::clip_grad_norm_ without the host sync ---- */
+/* One launch over every gradient in the list: x = g * unscale, sum of x^2 in a
+ * fixed (deterministic) order, non-finite detection, and -- unless
+ * RLCU_STAT_PARTIAL -- the finished record {norm, coef, found_inf, clip_active}
+ * written to `stat_out` (device).  Stands in for sum_sq_half_kernel /
+ * sum_sq_float_kernel + the blocking read-back + host sqrtf
+ * (include/training/trainer.h:103-133, 324-344); the scale kernels
+ * (trainer.h:136-145, 345-349) are folded into the update pass through `coef`.
+ *   unscale   : 1/loss_scale (times 1/world when gradients were summed); 1 for RL.cu
+ *   max_norm  : clip threshold; <= 0 disables clipping (trainer.h:280)
+ *   scaler    : optional device state; when given, unscale is taken as
+ *               grad_mul/scale from it (the `unscale` argument is ignored) and the
+ *               finished record also carries the step's bias corrections, after
+ *               which the scale / step counter are advanced.
+ * Calls on the same list must not overlap on the GPU (they share its scratch). */
+int rlcu_gradstat(rlcu_tensor_list* list, float unscale, float max_norm,
+                  rlcu_scaler_state* scaler, rlcu_stat* stat_out, uint32_t flags, void* stream);
+/* Completes a PARTIAL record after the caller has all-reduced stat->sum_sq. */
+int rlcu_gradstat_finalize(rlcu_stat* stat, float unscale, float max_norm,
+                           rlcu_scaler_state* scaler, void* stream);
+
+/* -------- update pass: AdamWOptimizer::step as one launch ---------------- */
+/* One launch over every tensor of the list (optimizer.h:119-147 issues three).
+ * `stat` may be NULL (no clip, no skip: the plain RL.cu update).  With `stat`,
+ * nothing is written when stat->found_inf, and every gradient is multiplied by
+ * stat->coef in registers first. */
+int rlcu_adamw_multi_step(rlcu_tensor_list* list, const rlcu_hparams* hp,
+                          const rlcu_stat* stat, uint32_t step_flags, void* stream);
+
+/* -------- host-side helpers --------------------------------------------- */
+/* 1 - powf(beta, t) in FP32 exactly as AdamWOptimizer::step (optimizer.h:121-122) */
+float rlcu_bias_correction(float beta, int step);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RLCU_ADAMW_H */

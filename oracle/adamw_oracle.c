@@ -1,0 +1,317 @@
+/*
+ * CPU oracle for the AdamW / gradient-clip optimizer path of RL.cu.
+ * TEST INFRASTRUCTURE ONLY -- see adamw_oracle.h for the parity status and the
+ * list of reference lines each function restates.
+ *
+ * Build: gcc -O2 -ffp-contract=off -mavx2 -mfma -fopenmp -shared -fPIC
+ * (-ffp-contract=off keeps the compiler from fusing on its own; the FUSED
+ * rounding model calls fmaf() explicitly where nvcc contracts the reference.)
+ */
+#include "adamw_oracle.h"
+
+#include <math.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* ------------------------------------------------------------------ */
+/* binary16 <-> binary32                                               */
+/* ------------------------------------------------------------------ */
+
+static inline uint32_t f32_bits(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+static inline float bits_f32(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+
+float orc_h2f(uint16_t h) {
+    uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    uint32_t exp = (h >> 10) & 0x1Fu;
+    uint32_t man = h & 0x3FFu;
+    if (exp == 0x1Fu) return bits_f32(sign | 0x7F800000u | (man << 13));   /* inf / NaN */
+    if (exp != 0) return bits_f32(sign | ((exp + 112u) << 23) | (man << 13));
+    if (man == 0) return bits_f32(sign);
+    /* subnormal: value = man * 2^-24, exact in binary32 */
+    float mag = (float)man * 5.9604644775390625e-08f;
+    return bits_f32(sign | f32_bits(mag));
+}
+
+uint16_t orc_f2h(float f) {
+    uint32_t x = f32_bits(f);
+    uint16_t sign = (uint16_t)((x >> 16) & 0x8000u);
+    uint32_t ax = x & 0x7FFFFFFFu;
+    if (ax >= 0x7F800000u) {                       /* inf or NaN */
+        if (ax == 0x7F800000u) return (uint16_t)(sign | 0x7C00u);
+        return (uint16_t)(sign | 0x7FFFu);         /* canonical NaN, as __float2half */
+    }
+    if (ax >= 0x477FF000u) return (uint16_t)(sign | 0x7C00u);  /* rounds to >= 65520 -> inf */
+    if (ax < 0x33000001u) return sign;             /* <= 2^-25 rounds to zero (tie to even) */
+    uint32_t e = ax >> 23;
+    uint32_t man = (ax & 0x7FFFFFu) | 0x800000u;   /* 24-bit significand */
+    uint32_t shift, half_exp;
+    if (e >= 113u) { shift = 13u; half_exp = e - 112u; }       /* normal binary16 */
+    else { shift = 126u - e; half_exp = 0u; }                  /* subnormal: 14..24 */
+    uint32_t q = man >> shift;
+    uint32_t rem = man & ((1u << shift) - 1u);
+    uint32_t halfway = 1u << (shift - 1u);
+    if (rem > halfway || (rem == halfway && (q & 1u))) q++;
+    /* normal: q has the implicit bit at 1<<10; adding (half_exp-1)<<10 merges it
+       and lets a mantissa carry bump the exponent.  subnormal: q is the field,
+       a carry to 1<<10 is exactly the smallest normal. */
+    uint32_t h = half_exp ? (((half_exp - 1u) << 10) + q) : q;
+    return (uint16_t)(sign | h);
+}
+
+void orc_f2h_array(const float* src, uint16_t* dst, int64_t n) {
+    for (int64_t i = 0; i < n; i++) dst[i] = orc_f2h(src[i]);
+}
+void orc_h2f_array(const uint16_t* src, float* dst, int64_t n) {
+    for (int64_t i = 0; i < n; i++) dst[i] = orc_h2f(src[i]);
+}
+
+/* ------------------------------------------------------------------ */
+/* the element update                                                  */
+/* ------------------------------------------------------------------ */
+
+float orc_bias_correction(float beta, int step) {
+    return 1.0f - powf(beta, (float)step);         /* optimizer.h:121-122 */
+}
+
+typedef struct { float lr, b1, b2, eps, wd, bc1_inv, bc2_inv; } orc_k;
+
+static inline orc_k make_k(float lr, float b1, float b2, float eps, float wd, float bc1, float bc2) {
+    orc_k k = { lr, b1, b2, eps, wd, 1.0f / bc1, 1.0f / bc2 };   /* adamw.cu:52-53 */
+    return k;
+}
+
+/* adamw.cu:24-36, every operation rounded on its own */
+static inline float upd_unfused(float w, float g, float* m, float* v, const orc_k* k) {
+    float mi = k->b1 * *m + (1.0f - k->b1) * g;
+    float vi = k->b2 * *v + (1.0f - k->b2) * g * g;
+    *m = mi; *v = vi;
+    float m_hat = mi * k->bc1_inv;
+    float v_hat = vi * k->bc2_inv;
+    return w * (1.0f - k->lr * k->wd) - k->lr * m_hat / (sqrtf(v_hat) + k->eps);
+}
+
+/* adamw.cu:24-36 with nvcc's default multiply-add contraction */
+static inline float upd_fused(float w, float g, float* m, float* v, const orc_k* k) {
+    float mi = fmaf(k->b1, *m, (1.0f - k->b1) * g);
+    float vi = fmaf(k->b2, *v, ((1.0f - k->b2) * g) * g);
+    *m = mi; *v = vi;
+    float m_hat = mi * k->bc1_inv;
+    float v_hat = vi * k->bc2_inv;
+    float decay = fmaf(-k->lr, k->wd, 1.0f);
+    float q = (k->lr * m_hat) / (sqrtf(v_hat) + k->eps);
+    return fmaf(w, decay, -q);
+}
+
+static inline float upd(float w, float g, float* m, float* v, const orc_k* k, int rounding) {
+    return rounding == ORC_FUSED ? upd_fused(w, g, m, v, k) : upd_unfused(w, g, m, v, k);
+}
+
+static int pick_threads(int threads) {
+#ifdef _OPENMP
+    if (threads <= 0) return omp_get_max_threads();
+    return threads;
+#else
+    (void)threads; return 1;
+#endif
+}
+
+void orc_adamw_fp16_master(float* master_w, uint16_t* model_w, const uint16_t* grad,
+                           float* m, float* v, int64_t n,
+                           float lr, float beta1, float beta2, float eps, float weight_decay,
+                           float bc1, float bc2, int rounding, int threads) {
+    if (n <= 0) return;                            /* adamw.cu:49 */
+    orc_k k = make_k(lr, beta1, beta2, eps, weight_decay, bc1, bc2);
+    int nt = pick_threads(threads);
+    #pragma omp parallel for num_threads(nt) schedule(static)
+    for (int64_t i = 0; i < n; i++) {
+        float w = upd(master_w[i], orc_h2f(grad[i]), &m[i], &v[i], &k, rounding);
+        master_w[i] = w;
+        model_w[i] = orc_f2h(w);
+    }
+}
+
+void orc_adamw_fp16(uint16_t* param, const uint16_t* grad, float* m, float* v, int64_t n,
+                    float lr, float beta1, float beta2, float eps, float weight_decay,
+                    float bc1, float bc2, int rounding, int threads) {
+    if (n <= 0) return;
+    orc_k k = make_k(lr, beta1, beta2, eps, weight_decay, bc1, bc2);
+    int nt = pick_threads(threads);
+    #pragma omp parallel for num_threads(nt) schedule(static)
+    for (int64_t i = 0; i < n; i++) {
+        float w = upd(orc_h2f(param[i]), orc_h2f(grad[i]), &m[i], &v[i], &k, rounding);
+        param[i] = orc_f2h(w);
+    }
+}
+
+void orc_adamw_fp32(float* w, const float* grad, float* m, float* v, int64_t n,
+                    float lr, float beta1, float beta2, float eps, float weight_decay,
+                    float bc1, float bc2, int rounding, int threads) {
+    if (n <= 0) return;                            /* adamw.cu:99 */
+    orc_k k = make_k(lr, beta1, beta2, eps, weight_decay, bc1, bc2);
+    int nt = pick_threads(threads);
+    #pragma omp parallel for num_threads(nt) schedule(static)
+    for (int64_t i = 0; i < n; i++)
+        w[i] = upd(w[i], grad[i], &m[i], &v[i], &k, rounding);
+}
+
+/* ------------------------------------------------------------------ */
+/* gradient norm and clip                                              */
+/* ------------------------------------------------------------------ */
+
+double orc_sum_sq_half(const uint16_t* g, int64_t n, float unscale, int threads) {
+    double s = 0.0;
+    int nt = pick_threads(threads);
+    #pragma omp parallel for num_threads(nt) schedule(static) reduction(+:s)
+    for (int64_t i = 0; i < n; i++) {
+        float x = orc_h2f(g[i]) * unscale;         /* trainer.h:108-109, FP32 product */
+        float sq = x * x;
+        if (isfinite(sq)) s += (double)sq;
+    }
+    return s;
+}
+
+double orc_sum_sq_float(const float* g, int64_t n, float unscale, int threads) {
+    double s = 0.0;
+    int nt = pick_threads(threads);
+    #pragma omp parallel for num_threads(nt) schedule(static) reduction(+:s)
+    for (int64_t i = 0; i < n; i++) {
+        float x = g[i] * unscale;                  /* trainer.h:125-126 */
+        float sq = x * x;
+        if (isfinite(sq)) s += (double)sq;
+    }
+    return s;
+}
+
+int64_t orc_count_nonfinite_half(const uint16_t* g, int64_t n) {
+    int64_t c = 0;
+    for (int64_t i = 0; i < n; i++) c += ((g[i] & 0x7C00u) == 0x7C00u);
+    return c;
+}
+
+int64_t orc_count_nonfinite_float(const float* g, int64_t n) {
+    int64_t c = 0;
+    for (int64_t i = 0; i < n; i++) c += ((f32_bits(g[i]) & 0x7F800000u) == 0x7F800000u);
+    return c;
+}
+
+void orc_scale_half(uint16_t* g, int64_t n, float scale, int threads) {
+    int nt = pick_threads(threads);
+    #pragma omp parallel for num_threads(nt) schedule(static)
+    for (int64_t i = 0; i < n; i++) g[i] = orc_f2h(orc_h2f(g[i]) * scale);   /* trainer.h:138 */
+}
+
+void orc_scale_float(float* g, int64_t n, float scale, int threads) {
+    int nt = pick_threads(threads);
+    #pragma omp parallel for num_threads(nt) schedule(static)
+    for (int64_t i = 0; i < n; i++) g[i] *= scale;                           /* trainer.h:144 */
+}
+
+float orc_clip_grad_norm(uint16_t* half_pool, int64_t n16, float* float_pool, int64_t n32,
+                         float max_norm, int threads) {
+    double s = 0.0;
+    if (n16 > 0) s += orc_sum_sq_half(half_pool, n16, 1.0f, threads);
+    if (n32 > 0) s += orc_sum_sq_float(float_pool, n32, 1.0f, threads);
+    float sum_sq = (float)s;                       /* the device scalar is FP32, trainer.h:339 */
+    float total_norm = sqrtf(sum_sq);              /* trainer.h:341 */
+    if (total_norm > max_norm) {                   /* trainer.h:343 */
+        float scale = max_norm / (total_norm + 1e-6f);
+        if (n16 > 0) orc_scale_half(half_pool, n16, scale, threads);
+        if (n32 > 0) orc_scale_float(float_pool, n32, scale, threads);
+    }
+    return total_norm;
+}
+
+/* ------------------------------------------------------------------ */
+/* fused multi-tensor step (statistics pass + update pass)             */
+/* ------------------------------------------------------------------ */
+
+void orc_gradstat_finalize(double sum_sq, uint32_t found_inf, float unscale, float max_norm,
+                           orc_stat* out) {
+    out->sum_sq = sum_sq;
+    out->found_inf = found_inf ? 1u : 0u;
+    out->norm = sqrtf((float)sum_sq);
+    out->clip_active = 0u;
+    out->coef = unscale;
+    if (max_norm > 0.0f && out->norm > max_norm) {         /* trainer.h:280, 343-344 */
+        float scale = max_norm / (out->norm + 1e-6f);
+        out->coef = unscale * scale;
+        out->clip_active = 1u;
+    }
+}
+
+void orc_gradstat(const orc_tensor* t, uint64_t count, float unscale, float max_norm,
+                  double extra_sum_sq, uint32_t extra_found_inf, int threads,
+                  orc_stat* out) {
+    double s = extra_sum_sq;
+    uint32_t inf = extra_found_inf;
+    for (uint64_t k = 0; k < count; k++) {
+        if (t[k].n == 0 || (t[k].flags & ORC_FLAG_GRAD_ZERO)) continue;
+        if (t[k].dtype == ORC_F16) {
+            s += orc_sum_sq_half((const uint16_t*)t[k].grad, (int64_t)t[k].n, unscale, threads);
+            inf |= orc_count_nonfinite_half((const uint16_t*)t[k].grad, (int64_t)t[k].n) != 0;
+        } else {
+            s += orc_sum_sq_float((const float*)t[k].grad, (int64_t)t[k].n, unscale, threads);
+            inf |= orc_count_nonfinite_float((const float*)t[k].grad, (int64_t)t[k].n) != 0;
+        }
+    }
+    orc_gradstat_finalize(s, inf, unscale, max_norm, out);
+}
+
+int orc_multi_step(const orc_tensor* t, uint64_t count, const orc_hparams* hp,
+                   const orc_stat* stat, uint32_t step_flags, int rounding, int threads) {
+    float coef = 1.0f;
+    int round_clip = 0;
+    if (stat) {
+        if (stat->found_inf) return 1;             /* overflow: nothing is written */
+        coef = stat->coef;
+        round_clip = (step_flags & ORC_STEP_ROUND_CLIP_FP16) && stat->clip_active;
+    }
+    int nt = pick_threads(threads);
+    for (uint64_t k = 0; k < count; k++) {
+        const orc_tensor* d = &t[k];
+        if (d->n == 0 || (d->flags & ORC_FLAG_NORM_ONLY)) continue;
+        orc_k kk = make_k(hp->lr, hp->beta1, hp->beta2, hp->eps, d->weight_decay,
+                          hp->bias_correction1, hp->bias_correction2);
+        int zero = (d->flags & ORC_FLAG_GRAD_ZERO) != 0;
+        int64_t n = (int64_t)d->n;
+        if (d->dtype == ORC_F16) {
+            uint16_t* p = (uint16_t*)d->param;
+            const uint16_t* g = (const uint16_t*)d->grad;
+            #pragma omp parallel for num_threads(nt) schedule(static)
+            for (int64_t i = 0; i < n; i++) {
+                float x = zero ? 0.0f : orc_h2f(g[i]) * coef;
+                if (round_clip) x = orc_h2f(orc_f2h(x));   /* trainer.h:138 */
+                float w0 = d->master ? d->master[i] : orc_h2f(p[i]);
+                float w = upd(w0, x, &d->m[i], &d->v[i], &kk, rounding);
+                if (d->master) d->master[i] = w;
+                p[i] = orc_f2h(w);
+            }
+        } else {
+            float* p = (float*)d->param;
+            const float* g = (const float*)d->grad;
+            #pragma omp parallel for num_threads(nt) schedule(static)
+            for (int64_t i = 0; i < n; i++) {
+                float x = zero ? 0.0f : g[i] * coef;       /* trainer.h:144 */
+                p[i] = upd(p[i], x, &d->m[i], &d->v[i], &kk, rounding);
+            }
+        }
+    }
+    return 0;
+}
+
+void orc_scaler_update(orc_scaler* s, uint32_t found_inf, int growth_interval) {
+    if (found_inf) {
+        s->scale *= 0.5f;
+        s->growth_tracker = 0;
+        s->skipped += 1;
+    } else {
+        s->step += 1;
+        s->growth_tracker += 1;
+        if (s->growth_tracker >= growth_interval) {
+            s->scale *= 2.0f;
+            s->growth_tracker = 0;
+        }
+    }
+}

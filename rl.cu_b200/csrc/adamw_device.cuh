@@ -1,0 +1,162 @@
+// Device-side building blocks of the sm_100a optimizer step: wide global
+// accesses, FP16 packing, the AdamW element update and the block reduction.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace rlcu {
+
+constexpr int kThreads = 256;          // threads per CTA for every kernel here
+constexpr int kGroup = 8;              // elements one thread moves per access set
+constexpr int kChunk = 8192;           // elements per work item (= 4 groups per thread)
+constexpr int kGroupsPerThread = kChunk / (kThreads * kGroup);
+
+// Internal per-item bits kept above the public RLCU_TENSOR_* flags.
+constexpr uint32_t kItemKindMask = 0x3u << 8;   // 0 F16, 1 F16+master, 2 F32
+constexpr uint32_t kItemKindF16 = 0u << 8;
+constexpr uint32_t kItemKindF16Master = 1u << 8;
+constexpr uint32_t kItemKindF32 = 2u << 8;
+constexpr uint32_t kItemVec16 = 1u << 10;       // every pointer 16-byte aligned
+constexpr uint32_t kItemVec32 = 1u << 11;       // FP32 pointers 32-byte aligned too
+
+// One unit of work: at most kChunk consecutive elements of one tensor, with
+// every pointer already advanced to the first of them.  64 bytes so that a
+// thread fetches it with four 16-byte loads.
+struct __align__(64) WorkItem {
+    void* p;
+    const void* g;
+    float* m;
+    float* v;
+    float* master;
+    uint32_t count;
+    float wd;
+    uint32_t flags;      // RLCU_TENSOR_* | kItem*
+    uint32_t pad[3];
+};
+static_assert(sizeof(WorkItem) == 64, "WorkItem must be 64 bytes");
+
+struct StepConsts {
+    float lr, b1, b2, eps, bc1_inv, bc2_inv;
+};
+
+struct __align__(32) F8 {
+    float a[8];
+};
+
+// ---- global memory access -------------------------------------------------
+// m, v and the master copy are read once and written once per step and the
+// working set is far beyond L2, so every access is marked streaming (.cs).
+// B200 has 256-bit global loads and stores (ld/st.global.v8.f32, sm_100+);
+// they need 32-byte alignment, otherwise two 128-bit accesses are used.
+
+template <bool V32>
+__device__ __forceinline__ F8 ld_f8(const float* p) {
+    F8 r;
+    if constexpr (V32) {
+        asm volatile("ld.global.cs.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                     : "=f"(r.a[0]), "=f"(r.a[1]), "=f"(r.a[2]), "=f"(r.a[3]),
+                       "=f"(r.a[4]), "=f"(r.a[5]), "=f"(r.a[6]), "=f"(r.a[7])
+                     : "l"(p));
+    } else {
+        float4 x = __ldcs(reinterpret_cast<const float4*>(p));
+        float4 y = __ldcs(reinterpret_cast<const float4*>(p) + 1);
+        r.a[0] = x.x; r.a[1] = x.y; r.a[2] = x.z; r.a[3] = x.w;
+        r.a[4] = y.x; r.a[5] = y.y; r.a[6] = y.z; r.a[7] = y.w;
+    }
+    return r;
+}
+
+template <bool V32>
+__device__ __forceinline__ void st_f8(float* p, const F8& r) {
+    if constexpr (V32) {
+        asm volatile("st.global.cs.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                     :: "l"(p), "f"(r.a[0]), "f"(r.a[1]), "f"(r.a[2]), "f"(r.a[3]),
+                        "f"(r.a[4]), "f"(r.a[5]), "f"(r.a[6]), "f"(r.a[7])
+                     : "memory");
+    } else {
+        __stcs(reinterpret_cast<float4*>(p), make_float4(r.a[0], r.a[1], r.a[2], r.a[3]));
+        __stcs(reinterpret_cast<float4*>(p) + 1, make_float4(r.a[4], r.a[5], r.a[6], r.a[7]));
+    }
+}
+
+__device__ __forceinline__ uint4 ld_h8(const void* p) {
+    return __ldcs(reinterpret_cast<const uint4*>(p));
+}
+
+__device__ __forceinline__ void st_h8(void* p, uint4 x) {
+    __stcs(reinterpret_cast<uint4*>(p), x);
+}
+
+__device__ __forceinline__ F8 h8_to_f8(uint4 x) {
+    F8 r;
+    const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+        float2 f = __half22float2(h);
+        r.a[2 * i] = f.x;
+        r.a[2 * i + 1] = f.y;
+    }
+    return r;
+}
+
+__device__ __forceinline__ uint4 f8_to_h8(const F8& r) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        __half2 h = __floats2half2_rn(r.a[2 * i], r.a[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// ---- arithmetic -------------------------------------------------------------
+// The AdamW element update of RL.cu (src/kernels/adamw.cu:25-36).  The
+// expressions are spelled with explicit round-to-nearest intrinsics in the
+// shape nvcc gives the reference source at its default -fmad=true, so the
+// result does not depend on what the compiler decides to contract here:
+//   m  = fma(b1, m, (1-b1)*g)          v = fma(b2, v, ((1-b2)*g)*g)
+//   w' = fma(w, fma(-lr, wd, 1), -((lr*m_hat) / (sqrt(v_hat) + eps)))
+// with IEEE division and square root (the reference is built without fast-math).
+__device__ __forceinline__ float adamw_element(float w, float g, float& m, float& v,
+                                               const StepConsts& c, float decay) {
+    const float mi = __fmaf_rn(c.b1, m, __fmul_rn(__fsub_rn(1.0f, c.b1), g));
+    const float vi = __fmaf_rn(c.b2, v, __fmul_rn(__fmul_rn(__fsub_rn(1.0f, c.b2), g), g));
+    m = mi;
+    v = vi;
+    const float m_hat = __fmul_rn(mi, c.bc1_inv);
+    const float v_hat = __fmul_rn(vi, c.bc2_inv);
+    const float q = __fdiv_rn(__fmul_rn(c.lr, m_hat), __fadd_rn(__fsqrt_rn(v_hat), c.eps));
+    return __fmaf_rn(w, decay, -q);
+}
+
+__device__ __forceinline__ float decay_factor(float lr, float wd) {
+    return __fmaf_rn(-lr, wd, 1.0f);   // 1 - lr*wd as nvcc contracts it
+}
+
+// What RL.cu's scale_half_kernel leaves in memory: g*scale rounded to FP16
+// (include/training/trainer.h:136-139).
+__device__ __forceinline__ float round_through_half(float x) {
+    return __half2float(__float2half_rn(x));
+}
+
+// ---- reduction --------------------------------------------------------------
+// Fixed-order sum over the CTA: xor-shuffle tree inside each warp, then the
+// warp results are added in warp order by thread 0.  Result valid in thread 0.
+__device__ __forceinline__ float block_sum(float x, float* smem /* kThreads/32 floats */) {
+#pragma unroll
+    for (int mask = 16; mask >= 1; mask >>= 1) x += __shfl_xor_sync(0xFFFFFFFFu, x, mask);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) smem[warp] = x;
+    __syncthreads();
+    float s = 0.0f;
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; w++) s += smem[w];
+    }
+    return s;
+}
+
+}  // namespace rlcu

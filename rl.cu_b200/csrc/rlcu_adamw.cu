@@ -1,0 +1,770 @@
+// sm_100a optimizer step for RL.cu: kernels and the C ABI declared in
+// include/rlcu_adamw.h.
+//
+// Two kernels carry the step:
+//   gradstat_kernel : reads every gradient once (2 B/param for FP16), produces
+//                     sum of squares, non-finite flag, norm and clip factor in
+//                     device memory.  Replaces RL.cu's sum_sq_* kernels, its
+//                     blocking read-back and host sqrtf
+//                     (include/training/trainer.h:103-133, 324-344).
+//   adamw_kernel    : one persistent launch over a table of work items that
+//                     covers every tensor; reads p/g/m/v (12 B/param) and
+//                     writes p/m/v (10 B/param).  Replaces RL.cu's three
+//                     launch_adamw_* calls and its two scale kernels
+//                     (include/training/optimizer.h:119-147,
+//                      src/kernels/adamw.cu, trainer.h:136-145, 345-349).
+// Both are pure streaming kernels bound by HBM bandwidth: CUDA cores only,
+// 128/256-bit coalesced accesses, grids sized to the SM count.
+#include "rlcu_adamw.h"
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <vector>
+
+#include "adamw_device.cuh"
+#include "host_util.h"
+
+namespace rlcu {
+
+// ---------------------------------------------------------------------------
+// update pass
+// ---------------------------------------------------------------------------
+
+struct GradXform {
+    float coef;        // multiply every gradient by this
+    bool round_half;   // then round FP16 gradients through binary16
+    bool zero_grads;   // write zeros over the gradient after reading it
+};
+
+template <bool ROUND>
+__device__ __forceinline__ float xform_h(float g, float coef) {
+    float x = __fmul_rn(g, coef);
+    if constexpr (ROUND) x = round_through_half(x);
+    return x;
+}
+
+// One group of 8 FP16 elements with every access vectorised.
+//   KIND 0: weight read from the FP16 parameter; KIND 1: from the FP32 master.
+template <int KIND, bool V32, bool ROUND, int U>
+__device__ __forceinline__ void f16_groups(const WorkItem& it, int first_group, int group_stride,
+                                           const StepConsts& c, float decay, const GradXform& xf) {
+    uint4 gw[U], pw[U];
+    F8 m[U], v[U], w[U];
+    const bool zero = (it.flags & RLCU_TENSOR_GRAD_ZERO) != 0;
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+        const size_t e = (size_t)(first_group + u * group_stride) * kGroup;
+        gw[u] = zero ? make_uint4(0, 0, 0, 0) : ld_h8(static_cast<const __half*>(it.g) + e);
+        if constexpr (KIND == 0) pw[u] = ld_h8(static_cast<const __half*>(it.p) + e);
+        else w[u] = ld_f8<V32>(it.master + e);
+        m[u] = ld_f8<V32>(it.m + e);
+        v[u] = ld_f8<V32>(it.v + e);
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+        const size_t e = (size_t)(first_group + u * group_stride) * kGroup;
+        F8 g = h8_to_f8(gw[u]);
+        if constexpr (KIND == 0) w[u] = h8_to_f8(pw[u]);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float x = xform_h<ROUND>(g.a[i], xf.coef);
+            w[u].a[i] = adamw_element(w[u].a[i], x, m[u].a[i], v[u].a[i], c, decay);
+        }
+        st_f8<V32>(it.m + e, m[u]);
+        st_f8<V32>(it.v + e, v[u]);
+        if constexpr (KIND == 1) st_f8<V32>(it.master + e, w[u]);
+        st_h8(static_cast<__half*>(it.p) + e, f8_to_h8(w[u]));
+        if (xf.zero_grads && !zero)
+            st_h8(const_cast<__half*>(static_cast<const __half*>(it.g)) + e, make_uint4(0, 0, 0, 0));
+    }
+}
+
+template <bool V32, int U>
+__device__ __forceinline__ void f32_groups(const WorkItem& it, int first_group, int group_stride,
+                                           const StepConsts& c, float decay, const GradXform& xf) {
+    F8 g[U], m[U], v[U], w[U];
+    const bool zero = (it.flags & RLCU_TENSOR_GRAD_ZERO) != 0;
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+        const size_t e = (size_t)(first_group + u * group_stride) * kGroup;
+        if (zero) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) g[u].a[i] = 0.0f;
+        } else {
+            g[u] = ld_f8<V32>(static_cast<const float*>(it.g) + e);
+        }
+        w[u] = ld_f8<V32>(static_cast<const float*>(it.p) + e);
+        m[u] = ld_f8<V32>(it.m + e);
+        v[u] = ld_f8<V32>(it.v + e);
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+        const size_t e = (size_t)(first_group + u * group_stride) * kGroup;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float x = __fmul_rn(g[u].a[i], xf.coef);   // trainer.h:144
+            w[u].a[i] = adamw_element(w[u].a[i], x, m[u].a[i], v[u].a[i], c, decay);
+        }
+        st_f8<V32>(it.m + e, m[u]);
+        st_f8<V32>(it.v + e, v[u]);
+        st_f8<V32>(static_cast<float*>(it.p) + e, w[u]);
+        if (xf.zero_grads && !zero) {
+            F8 z;
+#pragma unroll
+            for (int i = 0; i < 8; i++) z.a[i] = 0.0f;
+            st_f8<V32>(const_cast<float*>(static_cast<const float*>(it.g)) + e, z);
+        }
+    }
+}
+
+// Element-at-a-time path: ragged tails and tensors whose pointers are not
+// 16-byte aligned.  Same arithmetic, scalar accesses.
+__device__ __forceinline__ void scalar_range(const WorkItem& it, uint32_t begin, uint32_t end,
+                                             const StepConsts& c, float decay, const GradXform& xf) {
+    const uint32_t kind = it.flags & kItemKindMask;
+    const bool zero = (it.flags & RLCU_TENSOR_GRAD_ZERO) != 0;
+    for (uint32_t i = begin + threadIdx.x; i < end; i += kThreads) {
+        float m = it.m[i], v = it.v[i];
+        if (kind == kItemKindF32) {
+            float* p = static_cast<float*>(it.p);
+            float* g = const_cast<float*>(static_cast<const float*>(it.g));
+            const float x = zero ? 0.0f : __fmul_rn(g[i], xf.coef);
+            p[i] = adamw_element(p[i], x, m, v, c, decay);
+            if (xf.zero_grads && !zero) g[i] = 0.0f;
+        } else {
+            __half* p = static_cast<__half*>(it.p);
+            __half* g = const_cast<__half*>(static_cast<const __half*>(it.g));
+            float x = zero ? 0.0f : __fmul_rn(__half2float(g[i]), xf.coef);
+            if (xf.round_half) x = round_through_half(x);
+            const float w0 = (kind == kItemKindF16Master) ? it.master[i] : __half2float(p[i]);
+            const float w = adamw_element(w0, x, m, v, c, decay);
+            if (kind == kItemKindF16Master) it.master[i] = w;
+            p[i] = __float2half_rn(w);
+            if (xf.zero_grads && !zero) g[i] = __float2half_rn(0.0f);
+        }
+        it.m[i] = m;
+        it.v[i] = v;
+    }
+}
+
+template <int KIND, bool V32, bool ROUND>
+__device__ __forceinline__ void vector_item(const WorkItem& it, const StepConsts& c, float decay,
+                                            const GradXform& xf) {
+    const int groups = it.count / kGroup;
+    if (it.count == kChunk) {
+        // full item: every thread owns kGroupsPerThread groups, loads issued two groups deep
+        constexpr int U = 2;
+#pragma unroll
+        for (int b = 0; b < kGroupsPerThread / U; b++) {
+            const int first = threadIdx.x + b * U * kThreads;
+            if constexpr (KIND == 2) f32_groups<V32, U>(it, first, kThreads, c, decay, xf);
+            else f16_groups<KIND, V32, ROUND, U>(it, first, kThreads, c, decay, xf);
+        }
+    } else {
+        for (int grp = threadIdx.x; grp < groups; grp += kThreads) {
+            if constexpr (KIND == 2) f32_groups<V32, 1>(it, grp, 0, c, decay, xf);
+            else f16_groups<KIND, V32, ROUND, 1>(it, grp, 0, c, decay, xf);
+        }
+        scalar_range(it, groups * kGroup, it.count, c, decay, xf);
+    }
+}
+
+__device__ __forceinline__ void process_item(const WorkItem& it, const StepConsts& c,
+                                             const GradXform& xf) {
+    if (it.flags & RLCU_TENSOR_NORM_ONLY) return;
+    const float decay = decay_factor(c.lr, it.wd);
+    const uint32_t kind = it.flags & kItemKindMask;
+    if (!(it.flags & kItemVec16)) {
+        scalar_range(it, 0, it.count, c, decay, xf);
+        return;
+    }
+    const bool v32 = (it.flags & kItemVec32) != 0;
+    if (kind == kItemKindF16) {
+        if (xf.round_half) {
+            if (v32) vector_item<0, true, true>(it, c, decay, xf);
+            else vector_item<0, false, true>(it, c, decay, xf);
+        } else {
+            if (v32) vector_item<0, true, false>(it, c, decay, xf);
+            else vector_item<0, false, false>(it, c, decay, xf);
+        }
+    } else if (kind == kItemKindF16Master) {
+        if (xf.round_half) {
+            if (v32) vector_item<1, true, true>(it, c, decay, xf);
+            else vector_item<1, false, true>(it, c, decay, xf);
+        } else {
+            if (v32) vector_item<1, true, false>(it, c, decay, xf);
+            else vector_item<1, false, false>(it, c, decay, xf);
+        }
+    } else {
+        if (v32) vector_item<2, true, false>(it, c, decay, xf);
+        else vector_item<2, false, false>(it, c, decay, xf);
+    }
+}
+
+__device__ __forceinline__ WorkItem load_item(const WorkItem* table, uint32_t idx) {
+    // four 16-byte loads through the read-only path; the table is re-read every
+    // step and shared by all CTAs, so it is left to the default cache policy
+    WorkItem it;
+    const uint4* src = reinterpret_cast<const uint4*>(table + idx);
+    uint4* dst = reinterpret_cast<uint4*>(&it);
+#pragma unroll
+    for (int i = 0; i < 4; i++) dst[i] = __ldg(src + i);
+    return it;
+}
+
+// Resolves the per-launch constants from the statistics record (if any).
+// Returns false when the step must be skipped.
+__device__ __forceinline__ bool resolve_step(const rlcu_stat* stat, uint32_t step_flags,
+                                             StepConsts& c, GradXform& xf) {
+    xf.coef = 1.0f;
+    xf.round_half = false;
+    xf.zero_grads = (step_flags & RLCU_STEP_ZERO_GRADS) != 0;
+    if (stat) {
+        if (stat->found_inf) return false;
+        xf.coef = stat->coef;
+        xf.round_half = (step_flags & RLCU_STEP_ROUND_CLIP_FP16) && stat->clip_active;
+        if (step_flags & RLCU_STEP_DEVICE_BIAS_CORRECTION) {
+            c.bc1_inv = __fdiv_rn(1.0f, stat->bias_correction1);
+            c.bc2_inv = __fdiv_rn(1.0f, stat->bias_correction2);
+        }
+    }
+    return true;
+}
+
+// Multi-tensor update: persistent CTAs walk the work table with a grid stride.
+__global__ void __launch_bounds__(kThreads)
+adamw_table_kernel(const WorkItem* __restrict__ table, uint32_t n_items, StepConsts c,
+                   const rlcu_stat* __restrict__ stat, uint32_t step_flags) {
+    GradXform xf;
+    if (!resolve_step(stat, step_flags, c, xf)) {
+        // overflowed step: parameters and moments stay as they are; stale
+        // gradients are still cleared if the caller asked for that
+        if (!(step_flags & RLCU_STEP_ZERO_GRADS)) return;
+        for (uint32_t idx = blockIdx.x; idx < n_items; idx += gridDim.x) {
+            const WorkItem it = load_item(table, idx);
+            if (it.flags & (RLCU_TENSOR_NORM_ONLY | RLCU_TENSOR_GRAD_ZERO)) continue;
+            if ((it.flags & kItemKindMask) == kItemKindF32) {
+                float* g = const_cast<float*>(static_cast<const float*>(it.g));
+                for (uint32_t i = threadIdx.x; i < it.count; i += kThreads) g[i] = 0.0f;
+            } else {
+                __half* g = const_cast<__half*>(static_cast<const __half*>(it.g));
+                for (uint32_t i = threadIdx.x; i < it.count; i += kThreads) g[i] = __float2half_rn(0.0f);
+            }
+        }
+        return;
+    }
+    uint32_t idx = blockIdx.x;
+    if (idx >= n_items) return;
+    WorkItem next = load_item(table, idx);
+    while (true) {
+        const WorkItem it = next;
+        const uint32_t nidx = idx + gridDim.x;
+        if (nidx < n_items) next = load_item(table, nidx);   // fetched under the data loads
+        process_item(it, c, xf);
+        if (nidx >= n_items) break;
+        idx = nidx;
+    }
+}
+
+// Single-tensor update (RL.cu's launch_adamw_* shape): the work items are
+// computed from one descriptor instead of being read from a table.
+__global__ void __launch_bounds__(kThreads)
+adamw_flat_kernel(WorkItem base, uint64_t n, StepConsts c) {
+    GradXform xf;
+    xf.coef = 1.0f;
+    xf.round_half = false;
+    xf.zero_grads = false;
+    const uint64_t n_items = (n + kChunk - 1) / kChunk;
+    const uint32_t kind = base.flags & kItemKindMask;
+    for (uint64_t idx = blockIdx.x; idx < n_items; idx += gridDim.x) {
+        const uint64_t off = idx * kChunk;
+        WorkItem it = base;
+        it.count = (uint32_t)((n - off) < (uint64_t)kChunk ? (n - off) : (uint64_t)kChunk);
+        it.m += off;
+        it.v += off;
+        if (it.master) it.master += off;
+        if (kind == kItemKindF32) {
+            it.p = static_cast<float*>(base.p) + off;
+            it.g = static_cast<const float*>(base.g) + off;
+        } else {
+            it.p = static_cast<__half*>(base.p) + off;
+            it.g = static_cast<const __half*>(base.g) + off;
+        }
+        process_item(it, c, xf);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+half_to_float_kernel(float* __restrict__ dst, const __half* __restrict__ src, uint64_t n, bool vec) {
+    const uint64_t stride = (uint64_t)gridDim.x * kThreads;
+    uint64_t tid = (uint64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (vec) {
+        const uint64_t groups = n / kGroup;
+        for (uint64_t gi = tid; gi < groups; gi += stride) {
+            F8 f = h8_to_f8(ld_h8(src + gi * kGroup));
+            st_f8<false>(dst + gi * kGroup, f);
+        }
+        for (uint64_t i = groups * kGroup + tid; i < n; i += stride) dst[i] = __half2float(src[i]);
+    } else {
+        for (uint64_t i = tid; i < n; i += stride) dst[i] = __half2float(src[i]);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// statistics pass
+// ---------------------------------------------------------------------------
+
+// 1 - beta^t as the host computes it (optimizer.h:121-122: FP32 powf).  pow is
+// evaluated in FP64 and rounded once, which reproduces a correctly rounded powf.
+__device__ __forceinline__ float bias_correction_dev(float beta, int step) {
+    const float p = (float)pow((double)beta, (double)step);
+    return __fsub_rn(1.0f, p);
+}
+
+// Turns a total sum of squares into the finished record and advances the
+// scaler state.  Runs in one thread.
+__device__ void finalize_stat(rlcu_stat* out, double sum_sq, float unscale, float max_norm,
+                              rlcu_scaler_state* scaler) {
+    const float s = (float)sum_sq;
+    const bool bad = !isfinite(s);
+    const float norm = __fsqrt_rn(s);                       // trainer.h:341
+    float coef = unscale;
+    uint32_t clip = 0;
+    if (!bad && max_norm > 0.0f && norm > max_norm) {      // trainer.h:280, 343
+        coef = __fmul_rn(unscale, __fdiv_rn(max_norm, __fadd_rn(norm, 1e-6f)));
+        clip = 1;
+    }
+    out->sum_sq = sum_sq;
+    out->norm = norm;
+    out->coef = coef;
+    out->found_inf = bad ? 1u : 0u;
+    out->clip_active = clip;
+    if (scaler) {
+        out->loss_scale = scaler->scale;
+        if (bad) {
+            scaler->scale = scaler->scale * 0.5f;
+            scaler->growth_tracker = 0;
+            scaler->skipped += 1;
+        } else {
+            scaler->step += 1;
+            scaler->growth_tracker += 1;
+            if (scaler->growth_tracker >= scaler->growth_interval) {
+                scaler->scale = scaler->scale * 2.0f;
+                scaler->growth_tracker = 0;
+            }
+        }
+        const int t = scaler->step > 0 ? scaler->step : 1;
+        out->step = t;
+        out->bias_correction1 = bias_correction_dev(scaler->beta1, t);
+        out->bias_correction2 = bias_correction_dev(scaler->beta2, t);
+    }
+}
+
+__device__ __forceinline__ float scaler_unscale(const rlcu_scaler_state* scaler) {
+    const float mul = scaler->grad_mul == 0.0f ? 1.0f : scaler->grad_mul;
+    return __fmul_rn(mul, __fdiv_rn(1.0f, scaler->scale));
+}
+
+__device__ __forceinline__ void accum_h8(uint4 x, float unscale, float (&acc)[4]) {
+    const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        const float a = f.x * unscale, b = f.y * unscale;
+        acc[i] = fmaf(a, a, acc[i]);
+        acc[i] = fmaf(b, b, acc[i]);
+    }
+}
+
+// Scratch layout: partials[grid] floats, then one uint32 arrival counter kept at
+// zero between launches (the last CTA to arrive resets it).
+__global__ void __launch_bounds__(kThreads)
+gradstat_kernel(const WorkItem* __restrict__ table, uint32_t n_items, float unscale_arg,
+                float max_norm, rlcu_scaler_state* scaler, rlcu_stat* out, uint32_t flags,
+                float* partials, unsigned int* counter) {
+    __shared__ float warp_sums[kThreads / 32];
+    __shared__ bool is_last;
+    const float unscale = scaler ? scaler_unscale(scaler) : unscale_arg;
+
+    // Non-finite values need no separate test: inf*inf = inf and NaN propagate
+    // through the sums (squares cannot cancel), so the total is non-finite
+    // exactly when some gradient is.
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (uint32_t idx = blockIdx.x; idx < n_items; idx += gridDim.x) {
+        // only g, count and flags are needed: words 0-1 (p,g) and 2.. (count, flags)
+        const WorkItem* wi = table + idx;
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(wi));        // p, g
+        const uint4 d = __ldg(reinterpret_cast<const uint4*>(wi) + 2);    // master, count, wd
+        const uint4 e = __ldg(reinterpret_cast<const uint4*>(wi) + 3);    // flags
+        const void* g = reinterpret_cast<const void*>(((uint64_t)a.w << 32) | a.z);
+        const uint32_t count = d.z;
+        const uint32_t fl = e.x;
+        if (fl & RLCU_TENSOR_GRAD_ZERO) continue;
+        const bool f32 = (fl & kItemKindMask) == kItemKindF32;
+        if (!(fl & kItemVec16)) {
+            for (uint32_t i = threadIdx.x; i < count; i += kThreads) {
+                const float x = (f32 ? static_cast<const float*>(g)[i]
+                                     : __half2float(static_cast<const __half*>(g)[i])) * unscale;
+                acc[0] = fmaf(x, x, acc[0]);
+            }
+        } else if (!f32) {
+            const __half* gh = static_cast<const __half*>(g);
+            if (count == kChunk) {
+                uint4 x[kGroupsPerThread];
+#pragma unroll
+                for (int u = 0; u < kGroupsPerThread; u++)
+                    x[u] = ld_h8(gh + (size_t)(threadIdx.x + u * kThreads) * kGroup);
+#pragma unroll
+                for (int u = 0; u < kGroupsPerThread; u++) accum_h8(x[u], unscale, acc);
+            } else {
+                const uint32_t groups = count / kGroup;
+                for (uint32_t grp = threadIdx.x; grp < groups; grp += kThreads)
+                    accum_h8(ld_h8(gh + (size_t)grp * kGroup), unscale, acc);
+                for (uint32_t i = groups * kGroup + threadIdx.x; i < count; i += kThreads) {
+                    const float x = __half2float(gh[i]) * unscale;
+                    acc[0] = fmaf(x, x, acc[0]);
+                }
+            }
+        } else {
+            const float* gf = static_cast<const float*>(g);
+            const uint32_t quads = count / 4;
+            for (uint32_t q = threadIdx.x; q < quads; q += kThreads) {
+                const float4 x = __ldcs(reinterpret_cast<const float4*>(gf) + q);
+                const float a0 = x.x * unscale, a1 = x.y * unscale, a2 = x.z * unscale, a3 = x.w * unscale;
+                acc[0] = fmaf(a0, a0, acc[0]);
+                acc[1] = fmaf(a1, a1, acc[1]);
+                acc[2] = fmaf(a2, a2, acc[2]);
+                acc[3] = fmaf(a3, a3, acc[3]);
+            }
+            for (uint32_t i = quads * 4 + threadIdx.x; i < count; i += kThreads) {
+                const float x = gf[i] * unscale;
+                acc[0] = fmaf(x, x, acc[0]);
+            }
+        }
+    }
+    const float mine = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    const float block_total = block_sum(mine, warp_sums);
+
+    if (threadIdx.x == 0) {
+        partials[blockIdx.x] = block_total;
+        __threadfence();
+        const unsigned int ticket = atomicAdd(counter, 1u);
+        is_last = (ticket == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+
+    // last CTA to arrive: add the per-CTA partials in index order, in FP64
+    __threadfence();
+    if (threadIdx.x < 32) {
+        double s = 0.0;
+        for (uint32_t i = threadIdx.x; i < gridDim.x; i += 32)
+            s += (double)__ldcg(partials + i);
+#pragma unroll
+        for (int mask = 16; mask >= 1; mask >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, mask);
+        if (threadIdx.x == 0) {
+            *counter = 0;
+            if (flags & RLCU_STAT_PARTIAL) out->sum_sq = s;
+            else finalize_stat(out, s, unscale, max_norm, scaler);
+        }
+    }
+}
+
+__global__ void finalize_kernel(rlcu_stat* stat, float unscale_arg, float max_norm,
+                                rlcu_scaler_state* scaler) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        const float unscale = scaler ? scaler_unscale(scaler) : unscale_arg;
+        finalize_stat(stat, stat->sum_sq, unscale, max_norm, scaler);
+    }
+}
+
+}  // namespace rlcu
+
+// ===========================================================================
+// host side
+// ===========================================================================
+
+using namespace rlcu;
+
+struct rlcu_tensor_list {
+    int device = -1;
+    WorkItem* d_items = nullptr;
+    uint32_t n_items = 0;
+    uint64_t numel = 0;        // elements the update pass touches
+    uint64_t stat_numel = 0;   // elements the statistics pass reads
+    float* d_partials = nullptr;
+    unsigned int* d_counter = nullptr;
+    int grid_update = 0;
+    int grid_stat = 0;
+};
+
+namespace {
+
+struct DeviceInfo {
+    int sms = 0;
+    int occ_table = 0, occ_flat = 0, occ_stat = 0;
+};
+
+// per-device launch geometry, looked up once per device
+int device_info(DeviceInfo* out) {
+    static DeviceInfo cache[64];
+    static bool have[64] = {};
+    static std::mutex mu;
+    int dev = 0;
+    RLCU_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return set_error(RLCU_ERR_UNSUPPORTED, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!have[dev]) {
+        DeviceInfo di;
+        RLCU_CUDA(cudaDeviceGetAttribute(&di.sms, cudaDevAttrMultiProcessorCount, dev));
+        RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&di.occ_table, adamw_table_kernel, kThreads, 0));
+        RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&di.occ_flat, adamw_flat_kernel, kThreads, 0));
+        RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&di.occ_stat, gradstat_kernel, kThreads, 0));
+        if (di.occ_table < 1 || di.occ_flat < 1 || di.occ_stat < 1)
+            return set_error(RLCU_ERR_CUDA, "kernel does not fit on an SM");
+        cache[dev] = di;
+        have[dev] = true;
+    }
+    *out = cache[dev];
+    return RLCU_OK;
+}
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// kind and alignment bits of one tensor
+int classify(const rlcu_tensor_desc& d, uint32_t* bits) {
+    uint32_t kind;
+    if (d.dtype == RLCU_F32) {
+        if (d.master) return set_error(RLCU_ERR_INVALID, "FP32 tensor with a master copy");
+        kind = kItemKindF32;
+    } else if (d.dtype == RLCU_F16) {
+        kind = d.master ? kItemKindF16Master : kItemKindF16;
+    } else {
+        return set_error(RLCU_ERR_INVALID, "unknown dtype %u", d.dtype);
+    }
+    const bool norm_only = d.flags & RLCU_TENSOR_NORM_ONLY;
+    const bool grad_zero = d.flags & RLCU_TENSOR_GRAD_ZERO;
+    if (!grad_zero && !d.grad) return set_error(RLCU_ERR_INVALID, "null gradient");
+    if (!norm_only && (!d.param || !d.m || !d.v)) return set_error(RLCU_ERR_INVALID, "null param/m/v");
+    const size_t esz = d.dtype == RLCU_F32 ? 4 : 2;
+    if ((d.grad && !aligned(d.grad, esz)) || (d.param && !aligned(d.param, esz)) ||
+        !aligned(d.m, 4) || !aligned(d.v, 4) || !aligned(d.master, 4))
+        return set_error(RLCU_ERR_INVALID, "pointer not aligned to its element size");
+    bool v16 = aligned(d.grad, 16), v32 = true;
+    if (!norm_only) {
+        v16 = v16 && aligned(d.param, 16) && aligned(d.m, 16) && aligned(d.v, 16) && aligned(d.master, 16);
+        v32 = aligned(d.m, 32) && aligned(d.v, 32) && aligned(d.master, 32);
+        if (d.dtype == RLCU_F32) v32 = v32 && aligned(d.param, 32) && aligned(d.grad, 32);
+    }
+    *bits = kind | (v16 ? kItemVec16 : 0u) | ((v16 && v32) ? kItemVec32 : 0u);
+    return RLCU_OK;
+}
+
+StepConsts make_consts(float lr, float b1, float b2, float eps, float bc1, float bc2) {
+    StepConsts c;
+    c.lr = lr; c.b1 = b1; c.b2 = b2; c.eps = eps;
+    c.bc1_inv = 1.0f / bc1;    // FP32 on the host, as src/kernels/adamw.cu:52-53
+    c.bc2_inv = 1.0f / bc2;
+    return c;
+}
+
+int launch_flat(const rlcu_tensor_desc& d, int64_t n, float lr, float b1, float b2, float eps,
+                float bc1, float bc2, void* stream) {
+    if (n <= 0) return RLCU_OK;                // adamw.cu:49, :99
+    uint32_t bits = 0;
+    int rc = classify(d, &bits);
+    if (rc) return rc;
+    DeviceInfo di;
+    rc = device_info(&di);
+    if (rc) return rc;
+    WorkItem base;
+    std::memset(&base, 0, sizeof(base));
+    base.p = d.param; base.g = d.grad; base.m = d.m; base.v = d.v; base.master = d.master;
+    base.wd = d.weight_decay;
+    base.flags = bits;
+    const uint64_t items = ((uint64_t)n + kChunk - 1) / kChunk;
+    const uint64_t cap = (uint64_t)di.sms * di.occ_flat;
+    const int grid = (int)(items < cap ? items : cap);
+    adamw_flat_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>(
+        base, (uint64_t)n, make_consts(lr, b1, b2, eps, bc1, bc2));
+    RLCU_CUDA(cudaGetLastError());
+    return RLCU_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int rlcu_abi_version(void) { return RLCU_ABI_VERSION; }
+
+const char* rlcu_last_error(void) { return rlcu::last_error(); }
+
+float rlcu_bias_correction(float beta, int step) {
+    return 1.0f - powf(beta, (float)step);     // optimizer.h:121-122
+}
+
+int rlcu_adamw_fp16_master(float* master_w, void* model_w, const void* grad, float* m, float* v,
+                           int64_t n, float lr, float beta1, float beta2, float eps,
+                           float weight_decay, float bc1, float bc2, void* stream) {
+    if (n <= 0) return RLCU_OK;
+    if (!master_w) return set_error(RLCU_ERR_INVALID, "null master");
+    rlcu_tensor_desc d = {model_w, grad, m, v, master_w, (uint64_t)n, weight_decay, RLCU_F16, 0, 0};
+    return launch_flat(d, n, lr, beta1, beta2, eps, bc1, bc2, stream);
+}
+
+int rlcu_adamw_fp16(void* param, const void* grad, float* m, float* v,
+                    int64_t n, float lr, float beta1, float beta2, float eps,
+                    float weight_decay, float bc1, float bc2, void* stream) {
+    if (n <= 0) return RLCU_OK;
+    rlcu_tensor_desc d = {param, grad, m, v, nullptr, (uint64_t)n, weight_decay, RLCU_F16, 0, 0};
+    return launch_flat(d, n, lr, beta1, beta2, eps, bc1, bc2, stream);
+}
+
+int rlcu_adamw_fp32(float* w, const float* grad, float* m, float* v,
+                    int64_t n, float lr, float beta1, float beta2, float eps,
+                    float weight_decay, float bc1, float bc2, void* stream) {
+    if (n <= 0) return RLCU_OK;
+    rlcu_tensor_desc d = {w, grad, m, v, nullptr, (uint64_t)n, weight_decay, RLCU_F32, 0, 0};
+    return launch_flat(d, n, lr, beta1, beta2, eps, bc1, bc2, stream);
+}
+
+int rlcu_half_to_float(float* dst, const void* src, int64_t n, void* stream) {
+    if (n <= 0) return RLCU_OK;
+    if (!dst || !src) return set_error(RLCU_ERR_INVALID, "null pointer");
+    DeviceInfo di;
+    int rc = device_info(&di);
+    if (rc) return rc;
+    const bool vec = aligned(dst, 16) && aligned(src, 16);
+    const uint64_t want = ((uint64_t)n + (uint64_t)kThreads * kGroup - 1) / ((uint64_t)kThreads * kGroup);
+    const uint64_t cap = (uint64_t)di.sms * 8;
+    half_to_float_kernel<<<(int)(want < cap ? want : cap), kThreads, 0, (cudaStream_t)stream>>>(
+        dst, static_cast<const __half*>(src), (uint64_t)n, vec);
+    RLCU_CUDA(cudaGetLastError());
+    return RLCU_OK;
+}
+
+int rlcu_tensor_list_create(const rlcu_tensor_desc* descs, uint64_t count, rlcu_tensor_list** out) {
+    if (!out) return set_error(RLCU_ERR_INVALID, "null out");
+    *out = nullptr;
+    if (count && !descs) return set_error(RLCU_ERR_INVALID, "null descriptor array");
+    DeviceInfo di;
+    int rc = device_info(&di);
+    if (rc) return rc;
+
+    std::vector<WorkItem> items;
+    uint64_t numel = 0, stat_numel = 0;
+    for (uint64_t k = 0; k < count; k++) {
+        const rlcu_tensor_desc& d = descs[k];
+        if (d.reserved != 0) return set_error(RLCU_ERR_INVALID, "tensor %llu: reserved field not zero", (unsigned long long)k);
+        if (d.flags & ~(uint32_t)(RLCU_TENSOR_NORM_ONLY | RLCU_TENSOR_GRAD_ZERO))
+            return set_error(RLCU_ERR_INVALID, "tensor %llu: unknown flags", (unsigned long long)k);
+        if (d.n == 0) continue;
+        uint32_t bits = 0;
+        rc = classify(d, &bits);
+        if (rc) return rc;
+        if (!(d.flags & RLCU_TENSOR_NORM_ONLY)) numel += d.n;
+        if (!(d.flags & RLCU_TENSOR_GRAD_ZERO)) stat_numel += d.n;
+        const size_t esz = d.dtype == RLCU_F32 ? 4 : 2;
+        for (uint64_t off = 0; off < d.n; off += kChunk) {
+            WorkItem it;
+            std::memset(&it, 0, sizeof(it));
+            it.p = d.param ? static_cast<char*>(d.param) + off * esz : nullptr;
+            it.g = d.grad ? static_cast<const char*>(d.grad) + off * esz : nullptr;
+            it.m = d.m ? d.m + off : nullptr;
+            it.v = d.v ? d.v + off : nullptr;
+            it.master = d.master ? d.master + off : nullptr;
+            it.count = (uint32_t)((d.n - off) < (uint64_t)kChunk ? (d.n - off) : (uint64_t)kChunk);
+            it.wd = d.weight_decay;
+            it.flags = d.flags | bits;
+            items.push_back(it);
+        }
+    }
+    if (items.size() > 0xFFFFFFFFull) return set_error(RLCU_ERR_UNSUPPORTED, "too many work items");
+
+    rlcu_tensor_list* L = new (std::nothrow) rlcu_tensor_list();
+    if (!L) return set_error(RLCU_ERR_INVALID, "out of host memory");
+    RLCU_CUDA(cudaGetDevice(&L->device));
+    L->n_items = (uint32_t)items.size();
+    L->numel = numel;
+    L->stat_numel = stat_numel;
+    const uint64_t cap_u = (uint64_t)di.sms * di.occ_table, cap_s = (uint64_t)di.sms * di.occ_stat;
+    L->grid_update = (int)(L->n_items < cap_u ? (L->n_items ? L->n_items : 1) : cap_u);
+    L->grid_stat = (int)(L->n_items < cap_s ? (L->n_items ? L->n_items : 1) : cap_s);
+
+    cudaError_t e = cudaSuccess;
+    if (L->n_items) {
+        e = cudaMalloc(&L->d_items, (size_t)L->n_items * sizeof(WorkItem));
+        if (e == cudaSuccess)
+            e = cudaMemcpy(L->d_items, items.data(), (size_t)L->n_items * sizeof(WorkItem), cudaMemcpyHostToDevice);
+    }
+    // scratch of the statistics pass: one float per CTA, then the arrival counter
+    const size_t part_bytes = (((size_t)cap_s * sizeof(float) + 255) / 256) * 256;
+    if (e == cudaSuccess) e = cudaMalloc(&L->d_partials, part_bytes + 256);
+    if (e == cudaSuccess) {
+        L->d_counter = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(L->d_partials) + part_bytes);
+        e = cudaMemset(L->d_partials, 0, part_bytes + 256);
+    }
+    if (e != cudaSuccess) {
+        cudaFree(L->d_items);
+        cudaFree(L->d_partials);
+        delete L;
+        return set_error(RLCU_ERR_CUDA, "tensor list allocation: %s", cudaGetErrorString(e));
+    }
+    *out = L;
+    return RLCU_OK;
+}
+
+int rlcu_tensor_list_destroy(rlcu_tensor_list* list) {
+    if (!list) return RLCU_OK;
+    cudaError_t e1 = cudaFree(list->d_items);
+    cudaError_t e2 = cudaFree(list->d_partials);
+    delete list;
+    if (e1 != cudaSuccess || e2 != cudaSuccess)
+        return set_error(RLCU_ERR_CUDA, "cudaFree: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+    return RLCU_OK;
+}
+
+uint64_t rlcu_tensor_list_numel(const rlcu_tensor_list* list) { return list ? list->numel : 0; }
+uint64_t rlcu_tensor_list_stat_numel(const rlcu_tensor_list* list) { return list ? list->stat_numel : 0; }
+uint64_t rlcu_tensor_list_work_items(const rlcu_tensor_list* list) { return list ? list->n_items : 0; }
+
+int rlcu_gradstat(rlcu_tensor_list* list, float unscale, float max_norm,
+                  rlcu_scaler_state* scaler, rlcu_stat* stat_out, uint32_t flags, void* stream) {
+    if (!list || !stat_out) return set_error(RLCU_ERR_INVALID, "null list or stat");
+    if (flags & ~(uint32_t)RLCU_STAT_PARTIAL) return set_error(RLCU_ERR_INVALID, "unknown flags");
+    if (!aligned(stat_out, 16)) return set_error(RLCU_ERR_INVALID, "stat record must be 16-byte aligned");
+    gradstat_kernel<<<list->grid_stat, kThreads, 0, (cudaStream_t)stream>>>(
+        list->d_items, list->n_items, unscale, max_norm, scaler, stat_out, flags,
+        list->d_partials, list->d_counter);
+    RLCU_CUDA(cudaGetLastError());
+    return RLCU_OK;
+}
+
+int rlcu_gradstat_finalize(rlcu_stat* stat, float unscale, float max_norm,
+                           rlcu_scaler_state* scaler, void* stream) {
+    if (!stat) return set_error(RLCU_ERR_INVALID, "null stat");
+    finalize_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(stat, unscale, max_norm, scaler);
+    RLCU_CUDA(cudaGetLastError());
+    return RLCU_OK;
+}
+
+int rlcu_adamw_multi_step(rlcu_tensor_list* list, const rlcu_hparams* hp,
+                          const rlcu_stat* stat, uint32_t step_flags, void* stream) {
+    if (!list || !hp) return set_error(RLCU_ERR_INVALID, "null list or hparams");
+    const uint32_t known = RLCU_STEP_ROUND_CLIP_FP16 | RLCU_STEP_DEVICE_BIAS_CORRECTION | RLCU_STEP_ZERO_GRADS;
+    if (step_flags & ~known) return set_error(RLCU_ERR_INVALID, "unknown step flags");
+    if ((step_flags & RLCU_STEP_DEVICE_BIAS_CORRECTION) && !stat)
+        return set_error(RLCU_ERR_INVALID, "device bias correction needs a statistics record");
+    if (list->n_items == 0) return RLCU_OK;
+    adamw_table_kernel<<<list->grid_update, kThreads, 0, (cudaStream_t)stream>>>(
+        list->d_items, list->n_items,
+        make_consts(hp->lr, hp->beta1, hp->beta2, hp->eps, hp->bias_correction1, hp->bias_correction2),
+        stat, step_flags);
+    RLCU_CUDA(cudaGetLastError());
+    return RLCU_OK;
+}
+
+}  // extern "C"
