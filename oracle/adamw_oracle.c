@@ -4,8 +4,8 @@
  * list of reference lines each function restates.
  *
  * Build: gcc -O2 -ffp-contract=off -mavx2 -mfma -fopenmp -shared -fPIC
- * (-ffp-contract=off keeps the compiler from fusing on its own; the FUSED
- * rounding model calls fmaf() explicitly where nvcc contracts the reference.)
+ * (-ffp-contract=off keeps the compiler from fusing on its own; the rounding
+ * models call fmaf() explicitly at the sites they contract.)
  */
 #include "adamw_oracle.h"
 
@@ -82,30 +82,26 @@ static inline orc_k make_k(float lr, float b1, float b2, float eps, float wd, fl
     return k;
 }
 
-/* adamw.cu:24-36, every operation rounded on its own */
-static inline float upd_unfused(float w, float g, float* m, float* v, const orc_k* k) {
-    float mi = k->b1 * *m + (1.0f - k->b1) * g;
-    float vi = k->b2 * *v + (1.0f - k->b2) * g * g;
-    *m = mi; *v = vi;
-    float m_hat = mi * k->bc1_inv;
-    float v_hat = vi * k->bc2_inv;
-    return w * (1.0f - k->lr * k->wd) - k->lr * m_hat / (sqrtf(v_hat) + k->eps);
-}
-
-/* adamw.cu:24-36 with nvcc's default multiply-add contraction */
-static inline float upd_fused(float w, float g, float* m, float* v, const orc_k* k) {
-    float mi = fmaf(k->b1, *m, (1.0f - k->b1) * g);
-    float vi = fmaf(k->b2, *v, ((1.0f - k->b2) * g) * g);
-    *m = mi; *v = vi;
-    float m_hat = mi * k->bc1_inv;
-    float v_hat = vi * k->bc2_inv;
-    float decay = fmaf(-k->lr, k->wd, 1.0f);
-    float q = (k->lr * m_hat) / (sqrtf(v_hat) + k->eps);
-    return fmaf(w, decay, -q);
-}
-
+/* adamw.cu:24-36 under a rounding model (see ORC_* in the header): each of the
+ * four multiply-add sites is either rounded twice or contracted into one fma. */
 static inline float upd(float w, float g, float* m, float* v, const orc_k* k, int rounding) {
-    return rounding == ORC_FUSED ? upd_fused(w, g, m, v, k) : upd_unfused(w, g, m, v, k);
+    const int m_mode = rounding & 3, v_mode = (rounding >> 2) & 3;
+    const int w_fused = (rounding >> 4) & 1, d_fused = (rounding >> 5) & 1;
+    const float omb1 = 1.0f - k->b1, omb2 = 1.0f - k->b2;
+    float mi, vi;
+    if (m_mode == 1) mi = fmaf(k->b1, *m, omb1 * g);          /* fma(b1, m, (1-b1)*g)   */
+    else if (m_mode == 2) mi = fmaf(omb1, g, k->b1 * *m);     /* fma(1-b1, g, b1*m)     */
+    else mi = k->b1 * *m + omb1 * g;
+    const float t = omb2 * g;                                 /* (1-b2)*g*g is left-assoc */
+    if (v_mode == 1) vi = fmaf(k->b2, *v, t * g);             /* fma(b2, v, t*g)        */
+    else if (v_mode == 2) vi = fmaf(t, g, k->b2 * *v);        /* fma(t, g, b2*v)        */
+    else vi = k->b2 * *v + t * g;
+    *m = mi; *v = vi;
+    const float m_hat = mi * k->bc1_inv;
+    const float v_hat = vi * k->bc2_inv;
+    const float decay = d_fused ? fmaf(-k->lr, k->wd, 1.0f) : 1.0f - k->lr * k->wd;
+    const float q = (k->lr * m_hat) / (sqrtf(v_hat) + k->eps);
+    return w_fused ? fmaf(w, decay, -q) : w * decay - q;
 }
 
 static int pick_threads(int threads) {

@@ -35,15 +35,21 @@
 extern "C" {
 #endif
 
-/* Rounding model of the floating-point expression tree.
- *   ORC_UNFUSED : every multiply and add rounds separately, like the
- *                 reference's host-side check loops (tests/test_adamw.cu:283-293).
- *   ORC_FUSED   : multiply-adds contracted the way nvcc contracts the
- *                 reference kernel source (adamw.cu:25-36) at its default
- *                 -fmad=true:  m = fma(b1, m, (1-b1)*g),
- *                 v = fma(b2, v, ((1-b2)*g)*g), decay = fma(-lr, wd, 1),
- *                 w = fma(w, decay, -(lr*m_hat)/(sqrtf(v_hat)+eps)). */
-enum { ORC_UNFUSED = 0, ORC_FUSED = 1 };
+/* Rounding model of the expression tree of adamw.cu:25-36.  A bit field: which
+ * of the four multiply-add sites is contracted into a single fma.
+ *   bits 0-1  m = b1*m + (1-b1)*g     0 two roundings, 1 fma(b1,m,.), 2 fma(1-b1,g,.)
+ *   bits 2-3  v = b2*v + (1-b2)*g*g   0 two roundings, 1 fma(b2,v,.), 2 fma((1-b2)*g,g,.)
+ *   bit  4    w*decay - q             1 fma(w,decay,-q)
+ *   bit  5    decay = 1 - lr*wd       1 fma(-lr,wd,1)
+ * ORC_UNFUSED is the reference's host-side check loop (tests/test_adamw.cu:283-293,
+ * built without FMA contraction).  ORC_NVCC is what the reference's CUDA kernel
+ * computes when src/kernels/adamw.cu is built for sm_100a with CUDA 12.9 at its
+ * default -fmad=true; it was found by matching that binary's output bit for bit
+ * on a B200 (fixtures under tests/golden/), not by reading machine code.  Bit 5
+ * cannot be told apart by any input tried (1 - lr*wd rounds the same both ways). */
+#define ORC_ROUNDING(m_mode, v_mode, w_fused, d_fused) \
+    ((m_mode) | ((v_mode) << 2) | ((w_fused) << 4) | ((d_fused) << 5))
+enum { ORC_UNFUSED = 0, ORC_NVCC = ORC_ROUNDING(2, 2, 0, 0) };
 
 /* element kinds and flags; binary-compatible with rlcu_tensor_desc */
 enum { ORC_F16 = 0, ORC_F32 = 1 };

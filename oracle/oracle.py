@@ -19,7 +19,15 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liboracle.so")
 REF_LIB_PATH = os.path.join(_HERE, "_ref", "libref_adamw.so")
 
-UNFUSED, FUSED = 0, 1
+UNFUSED = 0
+
+
+def rounding(m_mode, v_mode, w_fused, d_fused):
+    """ORC_ROUNDING bit field (see adamw_oracle.h)."""
+    return m_mode | (v_mode << 2) | (w_fused << 4) | (d_fused << 5)
+
+
+NVCC = rounding(2, 2, 0, 0)
 F16, F32 = 0, 1
 FLAG_NORM_ONLY, FLAG_GRAD_ZERO = 1, 2
 STEP_ROUND_CLIP_FP16 = 1
@@ -114,17 +122,17 @@ def bias_correction(beta: float, step: int) -> float:
 
 
 def adamw_fp16_master(master, model_w, grad, m, v, lr, beta1, beta2, eps, wd, bc1, bc2,
-                      rounding=FUSED, threads=1):
+                      rounding=NVCC, threads=1):
     lib().orc_adamw_fp16_master(_p(master), _p(model_w), _p(grad), _p(m), _p(v), master.size,
                                 lr, beta1, beta2, eps, wd, bc1, bc2, rounding, threads)
 
 
-def adamw_fp16(param, grad, m, v, lr, beta1, beta2, eps, wd, bc1, bc2, rounding=FUSED, threads=1):
+def adamw_fp16(param, grad, m, v, lr, beta1, beta2, eps, wd, bc1, bc2, rounding=NVCC, threads=1):
     lib().orc_adamw_fp16(_p(param), _p(grad), _p(m), _p(v), param.size,
                          lr, beta1, beta2, eps, wd, bc1, bc2, rounding, threads)
 
 
-def adamw_fp32(w, grad, m, v, lr, beta1, beta2, eps, wd, bc1, bc2, rounding=FUSED, threads=1):
+def adamw_fp32(w, grad, m, v, lr, beta1, beta2, eps, wd, bc1, bc2, rounding=NVCC, threads=1):
     lib().orc_adamw_fp32(_p(w), _p(grad), _p(m), _p(v), w.size,
                          lr, beta1, beta2, eps, wd, bc1, bc2, rounding, threads)
 
@@ -171,7 +179,7 @@ def gradstat_finalize(sum_sq_total, found_inf, unscale, max_norm) -> Stat:
     return out
 
 
-def multi_step(tensors, hp: HParams, stat: Stat | None, step_flags=0, rounding=FUSED, threads=1) -> int:
+def multi_step(tensors, hp: HParams, stat: Stat | None, step_flags=0, rounding=NVCC, threads=1) -> int:
     return lib().orc_multi_step(C.addressof(tensors), len(tensors), C.addressof(hp),
                                 C.addressof(stat) if stat is not None else None,
                                 step_flags, rounding, threads)
@@ -202,5 +210,6 @@ def ref_lib() -> C.CDLL:
         R.ref_launch_adamw_fp32.argtypes = [vp, vp, vp, vp, i32] + [f] * 7 + [vp]
         R.ref_grad_sum_sq.argtypes = [vp, i32, vp, i32, vp, C.POINTER(f)]
         R.ref_clip_grad_norm.argtypes = [vp, i32, vp, i32, f, vp, C.POINTER(f)]
+        R.ref_scale_grads.argtypes = [vp, i32, vp, i32, f]
         _ref = R
     return _ref

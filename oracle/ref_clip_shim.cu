@@ -46,4 +46,14 @@ int ref_clip_grad_norm(half* half_pool, int n16, float* float_pool, int n32,
     return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
+// trainer.h:345-349 alone: the reference's two scale kernels with a scale chosen by the caller.
+int ref_scale_grads(half* half_pool, int n16, float* float_pool, int n32, float scale) {
+    const int block = 256;
+    int g16 = (n16 + block - 1) / block;
+    int g32 = (n32 + block - 1) / block;
+    if (n16 > 0) scale_half_kernel<<<g16, block>>>(half_pool, scale, n16);
+    if (n32 > 0) scale_float_kernel<<<g32, block>>>(float_pool, scale, n32);
+    return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
 }  // extern "C"

@@ -113,27 +113,29 @@ __device__ __forceinline__ uint4 f8_to_h8(const F8& r) {
 }
 
 // ---- arithmetic -------------------------------------------------------------
-// The AdamW element update of RL.cu (src/kernels/adamw.cu:25-36).  The
-// expressions are spelled with explicit round-to-nearest intrinsics in the
-// shape nvcc gives the reference source at its default -fmad=true, so the
-// result does not depend on what the compiler decides to contract here:
-//   m  = fma(b1, m, (1-b1)*g)          v = fma(b2, v, ((1-b2)*g)*g)
-//   w' = fma(w, fma(-lr, wd, 1), -((lr*m_hat) / (sqrt(v_hat) + eps)))
+// The AdamW element update of RL.cu (src/kernels/adamw.cu:25-36).  Every
+// operation is spelled with an explicit round-to-nearest intrinsic, in exactly
+// the shape the reference's kernel has when that file is built for sm_100a with
+// CUDA 12.9 at its default -fmad=true (established by matching its output bit
+// for bit on a B200), so the result depends neither on this compiler's
+// contraction choices nor on how the loop around it is unrolled:
+//   m  = fma(1-b1, g, b1*m)            v  = fma((1-b2)*g, g, b2*v)
+//   w' = w*(1 - lr*wd) - (lr*m_hat) / (sqrt(v_hat) + eps)     (no fma here)
 // with IEEE division and square root (the reference is built without fast-math).
 __device__ __forceinline__ float adamw_element(float w, float g, float& m, float& v,
                                                const StepConsts& c, float decay) {
-    const float mi = __fmaf_rn(c.b1, m, __fmul_rn(__fsub_rn(1.0f, c.b1), g));
-    const float vi = __fmaf_rn(c.b2, v, __fmul_rn(__fmul_rn(__fsub_rn(1.0f, c.b2), g), g));
+    const float mi = __fmaf_rn(__fsub_rn(1.0f, c.b1), g, __fmul_rn(c.b1, m));
+    const float vi = __fmaf_rn(__fmul_rn(__fsub_rn(1.0f, c.b2), g), g, __fmul_rn(c.b2, v));
     m = mi;
     v = vi;
     const float m_hat = __fmul_rn(mi, c.bc1_inv);
     const float v_hat = __fmul_rn(vi, c.bc2_inv);
     const float q = __fdiv_rn(__fmul_rn(c.lr, m_hat), __fadd_rn(__fsqrt_rn(v_hat), c.eps));
-    return __fmaf_rn(w, decay, -q);
+    return __fsub_rn(__fmul_rn(w, decay), q);
 }
 
 __device__ __forceinline__ float decay_factor(float lr, float wd) {
-    return __fmaf_rn(-lr, wd, 1.0f);   // 1 - lr*wd as nvcc contracts it
+    return __fsub_rn(1.0f, __fmul_rn(lr, wd));   // 1 - lr*wd
 }
 
 // What RL.cu's scale_half_kernel leaves in memory: g*scale rounded to FP16
