@@ -1,0 +1,412 @@
+"""Benchmark of the optimizer step (statistics pass + multi-tensor AdamW update).
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload NAME]
+
+N = 1   : Qwen3-0.6B-shaped parameter set (596,049,920 FP16 parameters in 310 tensors,
+          FP32 moments warmed by 5 prior steps, global-norm clip at 1.0, lr 1e-6) updated
+          on one GPU.  One step = one statistics launch + one update launch.
+N > 1   : the same parameter set with the FP32 moments partitioned ZeRO-1 style over the N
+          ranks (launched by torch.distributed.run, one rank per GPU): NCCL reduce-scatter
+          of the FP16 gradients, sharded statistics + update, NCCL all-gather of the FP16
+          parameters.  Total work is fixed ("strong" scaling).
+
+Rank 0 prints one JSON line.  `value` is parameters updated per second with everything
+resident in HBM; `e2e` is the same step driven from host memory (the step's FP16 gradients
+copied from pinned host memory, the statistics record read back, both inside the timed
+region); `roofline` is the update kernel's algorithmic bytes (22 per parameter) over its
+CUDA-event time against the measured HBM copy bandwidth; `cpu_baseline` is the CPU
+restatement of the reference algorithm timed on this machine's cores.
+
+`--impl reference` times that CPU restatement (all host threads) instead of the GPU path.
+Data are synthetic (seeded normal values with the shapes above); no checkpoint is read.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+BYTES_PER_PARAM = 22          # read p,g (2+2) m,v (4+4); write p (2) m,v (4+4)
+FALLBACK_HBM_GBS = 6650.0
+NCU_DRAM_BYTES_PER_PARAM = 21.74
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def shapes_for(workload):
+    from helpers import qwen3_0p6b, qwen3_8b
+    if workload == "qwen3-0.6b":
+        return qwen3_0p6b()
+    if workload == "qwen3-8b":
+        return qwen3_8b()
+    if workload == "qwen3-0.6b-4l":     # 4 of the 28 layers + embedding: the profiler-sized case
+        from helpers import qwen3_shapes
+        return qwen3_shapes(1024, 3072, 4, 151936, 16, 8, 128, tied=True)
+    raise SystemExit(f"unknown workload {workload}")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def __enter__(self):
+        if self.nv:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def report(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "note": "NVML unavailable"}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def build_pools(torch, shapes, dev, seed):
+    """Flat pools in RL.cu's order with one descriptor per tensor.  FP16 params ~N(0,0.02)
+    with norm weights 1.0, FP16 grads ~N(0,1e-4), FP32 moments zero."""
+    total = sum(n for _, n, _ in shapes)
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    p = torch.empty(total, dtype=torch.float16, device=dev)
+    g = torch.empty(total, dtype=torch.float16, device=dev)
+    step = 1 << 26
+    for lo in range(0, total, step):
+        hi = min(total, lo + step)
+        p[lo:hi] = (torch.randn(hi - lo, device=dev, generator=gen) * 0.02).half()
+        g[lo:hi] = (torch.randn(hi - lo, device=dev, generator=gen) * 1e-4).half()
+    off = 0
+    for name, n, _ in shapes:
+        if "norm" in name:
+            p[off:off + n] = 1.0
+        off += n
+    m = torch.zeros(total, dtype=torch.float32, device=dev)
+    v = torch.zeros(total, dtype=torch.float32, device=dev)
+    return dict(p=p, g=g, m=m, v=v, total=total)
+
+
+def fresh_grads(torch, g, gen):
+    step = 1 << 26
+    for lo in range(0, g.numel(), step):
+        hi = min(g.numel(), lo + step)
+        g[lo:hi] = (torch.randn(hi - lo, device=g.device, generator=gen) * 1e-4).half()
+
+
+def make_descs(pkg, pools, shapes, wd):
+    descs, off = [], 0
+    for _, n, decays in shapes:
+        descs.append(pkg.TensorDesc(pools["p"].data_ptr() + 2 * off, pools["g"].data_ptr() + 2 * off,
+                                    pools["m"].data_ptr() + 4 * off, pools["v"].data_ptr() + 4 * off,
+                                    None, n, wd if decays else 0.0, pkg.F16, 0, 0))
+        off += n
+    return descs
+
+
+# ----------------------------------------------------------------------------------------
+# CPU restatement of the reference (the reported baseline and the `--impl reference` arm)
+# ----------------------------------------------------------------------------------------
+
+def cpu_port_step_rate(sample_params, steps, warmup, threads=0):
+    """Times gradient statistics + clip + AdamW of the CPU oracle on a slice of the workload."""
+    import numpy as np
+    from oracle import oracle as O
+    rng = np.random.default_rng(0)
+    n = sample_params
+    e = dict(p=O.f2h(rng.standard_normal(n, dtype=np.float32) * np.float32(0.02)),
+             g=O.f2h(rng.standard_normal(n, dtype=np.float32) * np.float32(1e-4 * (596_049_920 / n) ** 0.5)),
+             m=np.zeros(n, np.float32), v=np.zeros(n, np.float32), wd=0.01)
+    ts = O.make_tensors([e])
+    cores = os.cpu_count() if threads == 0 else threads
+    times = []
+    for i in range(warmup + steps):
+        t = 6 + i
+        hp = O.HParams(1e-6, 0.9, 0.999, 1e-8, O.bias_correction(0.9, t), O.bias_correction(0.999, t))
+        t0 = time.perf_counter()
+        st = O.gradstat(ts, 1.0, 1.0, threads=threads)
+        O.multi_step(ts, hp, st, O.STEP_ROUND_CLIP_FP16, O.NVCC, threads)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    return n / (sum(times) / len(times)), sum(times) / len(times), cores
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = 1 << 26
+    rate, sec, cores = cpu_port_step_rate(sample, args.steps, args.warmup, threads=0)
+    line = {
+        "impl": "reference", "metric": "adamw_params_per_sec", "value": rate, "unit": "params/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
+        "dtype": "f16 params/grads, f32 moments", "data": "synthetic",
+        "config": {"workload": workload_name(args), "sample_params": sample},
+        "cpu_baseline": {"value": rate, "unit": "params/s", "cores": cores, "kind": "port",
+                         "sample": f"{sample} parameters of the workload per step (statistics + clip + update), "
+                                   f"OpenMP over all host threads"},
+        "e2e": {"value": rate, "unit": "params/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_name(args):
+    base = {"qwen3-0.6b-4l": "Qwen3-0.6B shapes cut to 4 layers + embedding (profiling case), clip 1.0",
+            "qwen3-0.6b": "Qwen3-0.6B-shaped multi-tensor AdamW step, 596,049,920 params in 310 tensors, clip 1.0",
+            "qwen3-8b": "Qwen3-8B-shaped multi-tensor AdamW step, 8,190,735,360 params in 399 tensors, clip 1.0"}[args.workload]
+    if args.gpus > 1:
+        base += f", ZeRO-1 over {args.gpus} GPUs (reduce-scatter grads, sharded update, all-gather params)"
+    return base
+
+
+# ----------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------
+
+def run_single(args):
+    import numpy as np
+    import torch
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    shapes = shapes_for(args.workload)
+    pools = build_pools(torch, shapes, dev, seed=0)
+    P = pools["total"]
+    lr, b1, b2, eps, wd, max_norm = 1e-6, 0.9, 0.999, 1e-8, 0.01, 1.0
+    tl = pkg.TensorList(make_descs(pkg, pools, shapes, wd))
+    stat = torch.zeros(16, dtype=torch.float32, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    flags = pkg.STEP_ROUND_CLIP_FP16
+
+    def step(t):
+        tl.gradstat(stat.data_ptr(), 1.0, max_norm, stream=stream)
+        tl.step(pkg.hparams(lr, b1, b2, eps, t), stat.data_ptr(), flags, stream=stream)
+
+    # moments warmed by five prior steps on fresh gradients (untimed)
+    gen = torch.Generator(device=dev).manual_seed(1)
+    for t in range(1, 6):
+        fresh_grads(torch, pools["g"], gen)
+        step(t)
+    fresh_grads(torch, pools["g"], gen)
+    torch.cuda.synchronize()
+
+    t = 6
+    for _ in range(args.warmup):
+        step(t)
+        t += 1
+    torch.cuda.synchronize()
+
+    K = args.steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    with ClockSampler(0) as clocks:
+        torch.cuda.synchronize()
+        for k in range(K):
+            ev[k][0].record()
+            tl.gradstat(stat.data_ptr(), 1.0, max_norm, stream=stream)
+            ev[k][1].record()
+            tl.step(pkg.hparams(lr, b1, b2, eps, t), stat.data_ptr(), flags, stream=stream)
+            ev[k][2].record()
+            t += 1
+        torch.cuda.synchronize()
+    total_ms = ev[0][0].elapsed_time(ev[K - 1][2])
+    stat_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    upd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    ms_per_step = total_ms / K
+    value = P / (ms_per_step * 1e-3)
+    final = pkg.Stat.from_buffer_copy(stat.cpu().numpy().tobytes())
+
+    if args.quick:
+        print(json.dumps({"metric": "adamw_params_per_sec", "value": value, "unit": "params/s", "n_gpus": 1,
+                          "steps": K, "warmup": args.warmup, "ms_per_step": ms_per_step,
+                          "kernels_ms": {"gradstat_kernel": stat_ms, "adamw_table_kernel": upd_ms},
+                          "config": {"workload": workload_name(args), "params": P}, "quick": True}), flush=True)
+        return
+
+    # ---- end to end from host memory: H2D of the step's gradients, step, D2H of the record
+    host_g = torch.empty(P, dtype=torch.float16).pin_memory()
+    host_g.copy_(pools["g"])
+    host_stat = torch.empty(16, dtype=torch.float32).pin_memory()
+    e2e_steps = max(3, min(K, 20))
+
+    def e2e_step(tt):
+        pools["g"].copy_(host_g, non_blocking=True)
+        tl.gradstat(stat.data_ptr(), 1.0, max_norm, stream=stream)
+        tl.step(pkg.hparams(lr, b1, b2, eps, tt), stat.data_ptr(), flags, stream=stream)
+        host_stat.copy_(stat, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step(t)
+        t += 1
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step(t)
+        t += 1
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    assert pkg.Stat.from_buffer_copy(host_stat.numpy().tobytes()).found_inf == 0
+
+    # ---- the reference's own CUDA kernels on the same GPU (when they were built): context only
+    ref_cuda = None
+    try:
+        from oracle import oracle as O
+        if O.ref_available() and P < 2 ** 31:
+            ref_cuda = time_reference_cuda(torch, O, pools, shapes, lr, b1, b2, eps, wd, max_norm)
+    except Exception as exc:   # the checker is optional here
+        ref_cuda = {"unavailable": str(exc)[:120]}
+
+    peak, peak_kind = measured_peak()
+    achieved = BYTES_PER_PARAM * P / (upd_ms * 1e-3) / 1e9
+    # DRAM bytes per launch: 21.74 bytes per parameter measured with ncu
+    # (dram__bytes_read.sum + dram__bytes_write.sum) on a 218,507,264-parameter cut of this
+    # workload, scaled by the element count of this launch.
+    traffic = NCU_DRAM_BYTES_PER_PARAM * P
+
+    # ---- CPU restatement on this machine's cores (bounded sample)
+    cpu_rate, cpu_sec, cores = cpu_port_step_rate(1 << 25, 3, 1, threads=0)
+    cpu_rate_1t, _, _ = cpu_port_step_rate(1 << 22, 2, 1, threads=1)
+
+    line = {
+        "metric": "adamw_params_per_sec", "value": value, "unit": "params/s", "n_gpus": 1,
+        "steps": K, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16 params/grads, f32 moments and math",
+        "data": "synthetic",
+        "config": {"workload": workload_name(args), "params": P, "tensors": len(shapes),
+                   "launches_per_step": 2, "l2": "working set 7.2 GB per step, far larger than the 126 MB L2",
+                   "grad_norm": final.norm, "clip_active": int(final.clip_active)},
+        "kernels_ms": {"gradstat_kernel": stat_ms, "adamw_table_kernel": upd_ms},
+        "hbm_gbs_whole_step": (BYTES_PER_PARAM + 2) * P / (ms_per_step * 1e-3) / 1e9,
+        "roofline": {"bound": "hbm", "kernel": "adamw_table_kernel", "achieved": achieved, "peak": peak,
+                     "peak_kind": f"{peak_kind} copy bandwidth", "unit": "GB/s", "frac": achieved / peak,
+                     "frac_of_nominal_8000": achieved / 8000.0, "traffic": traffic,
+                     "algorithmic_bytes_per_launch": BYTES_PER_PARAM * P},
+        "e2e": {"value": P / (e2e_ms * 1e-3), "unit": "params/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": 2 * P, "d2h_bytes_per_step": 64,
+                "what": "pinned-host FP16 gradients copied in, statistics + update, statistics record copied out"},
+        "gpu_launches": 2 * K,
+        "clocks": clocks.report(),
+        "cpu_baseline": {"value": cpu_rate, "unit": "params/s", "cores": cores, "kind": "port",
+                         "sample": f"{1 << 25} parameters per step, 3 steps, statistics + clip + update, "
+                                   f"OpenMP over all host threads; single thread: {cpu_rate_1t:.3e} params/s"},
+    }
+    if ref_cuda is not None:
+        line["reference_cuda_same_gpu"] = ref_cuda
+    print(json.dumps(line), flush=True)
+
+
+def time_reference_cuda(torch, O, pools, shapes, lr, b1, b2, eps, wd, max_norm):
+    """RL.cu's own sequence (sum of squares, read-back, scale, launch_adamw_fp16 with FP32
+    master) on the same FP16 pools, timed with CUDA events.  28 bytes per parameter in the
+    update plus the read-back stall; shown beside the new path for context."""
+    R = O.ref_lib()
+    P = pools["total"]
+    master = pools["p"].float()
+    p, m, v = pools["p"].clone(), pools["m"].clone(), pools["v"].clone()
+    g0 = pools["g"]
+    g = g0.clone()
+    acc = torch.zeros(1, device=g.device)
+    norm = C.c_float()
+    bc1, bc2 = O.bias_correction(b1, 7), O.bias_correction(b2, 7)
+
+    def step():
+        g.copy_(g0)       # the reference scales gradients in place; restore (untimed below)
+    times = []
+    for i in range(8):
+        step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        R.ref_clip_grad_norm(g.data_ptr(), P, None, 0, max_norm, acc.data_ptr(), C.byref(norm))
+        R.ref_launch_adamw_fp16(master.data_ptr(), p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(),
+                                P, lr, b1, b2, eps, wd, bc1, bc2, None)
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            times.append(e0.elapsed_time(e1))
+    ms = statistics.mean(times)
+    return {"ms_per_step": ms, "value": P / (ms * 1e-3), "unit": "params/s",
+            "what": "RL.cu kernels rebuilt for sm_100a: sum_sq + D2H + scale + launch_adamw_fp16 (FP32 master)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="qwen3-0.6b", choices=["qwen3-0.6b", "qwen3-8b", "qwen3-0.6b-4l"])
+    ap.add_argument("--quick", action="store_true",
+                    help="device-resident timing only (no end-to-end, CPU or reference-kernel legs): for profiler runs")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        run_single(args)
+    else:
+        from bench_zero1 import run_sharded   # noqa: WPS433  (needs torch.distributed)
+        run_sharded(args)
+
+
+if __name__ == "__main__":
+    main()
