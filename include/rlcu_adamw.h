@@ -190,6 +190,26 @@ uint64_t rlcu_tensor_list_work_items(const rlcu_tensor_list* list);
  * Calls on the same list must not overlap on the GPU (they share its scratch). */
 int rlcu_gradstat(rlcu_tensor_list* list, float unscale, float max_norm,
                   rlcu_scaler_state* scaler, rlcu_stat* stat_out, uint32_t flags, void* stream);
+/* The statistics pass for callers that cannot allocate device memory: one flat
+ * gradient buffer in (RL.cu's half_pool or float_pool), the finished record
+ * {sum_sq, norm, coef, found_inf, clip_active} out, no tensor list and no
+ * allocation anywhere -- the reduction scratch is a fixed 1 MiB array inside the
+ * library image, resident on every GPU that loads the library.  This entry
+ * point has no counterpart in RL.cu.  It exists because RL.cu's trainer runs
+ * beside an inference engine that claims the free device memory for its KV
+ * cache, so an optimizer step issued at that point cannot rely on cudaMalloc,
+ * and because some hot paths are not allowed to enter the allocator at all.
+ *   n      : at most RLCU_NOALLOC_MAX_ELEMS; more is refused with RLCU_ERR_INVALID
+ *   dtype  : RLCU_F16 or RLCU_F32
+ * Calls on one device share the scratch: calls that overlap on the GPU race.
+ * The first call on a device resolves the scratch address; make it at set-up,
+ * before any stream capture.  Sums are taken per 8192-element chunk and added in
+ * chunk order, so the result does not depend on the GPU's SM count; it agrees
+ * with rlcu_gradstat to rounding (1e-5 relative on the norm), not bit for bit. */
+#define RLCU_NOALLOC_MAX_ELEMS 2147483648ull
+int rlcu_gradstat_flat_noalloc(const void* grad, uint32_t dtype, uint64_t n,
+                               float unscale, float max_norm,
+                               rlcu_stat* stat_out, void* stream);
 /* Completes a PARTIAL record after the caller has all-reduced stat->sum_sq. */
 int rlcu_gradstat_finalize(rlcu_stat* stat, float unscale, float max_norm,
                            rlcu_scaler_state* scaler, void* stream);

@@ -32,8 +32,9 @@ EXPORTS = [
     "rlcu_adamw_fp32", "rlcu_half_to_float", "rlcu_tensor_list_create",
     "rlcu_tensor_list_destroy", "rlcu_tensor_list_numel", "rlcu_tensor_list_stat_numel",
     "rlcu_tensor_list_work_items", "rlcu_gradstat", "rlcu_gradstat_finalize",
-    "rlcu_adamw_multi_step", "rlcu_bias_correction",
+    "rlcu_adamw_multi_step", "rlcu_bias_correction", "rlcu_gradstat_flat_noalloc",
 ]
+NOALLOC_MAX_ELEMS = 1 << 31
 # C++-linkage launchers with RL.cu's signatures (include/kernels/adamw.cuh)
 CXX_EXPORTS = [
     "_Z17launch_adamw_fp16PfP6__halfPKS0_S_S_ifffffffP11CUstream_st",
@@ -116,6 +117,7 @@ def lib() -> C.CDLL:
     L.rlcu_gradstat.argtypes = [vp, f, f, vp, vp, u32, vp]
     L.rlcu_gradstat_finalize.argtypes = [vp, f, f, vp, vp]
     L.rlcu_adamw_multi_step.argtypes = [vp, vp, vp, u32, vp]
+    L.rlcu_gradstat_flat_noalloc.argtypes = [vp, u32, u64, f, f, vp, vp]
     L.rlcu_bias_correction.argtypes = [f, C.c_int]
     L.rlcu_bias_correction.restype = f
     _lib = L
@@ -197,3 +199,10 @@ class TensorList:
 
 def gradstat_finalize(stat_ptr, unscale=1.0, max_norm=0.0, scaler_ptr=None, stream=None):
     check(lib().rlcu_gradstat_finalize(stat_ptr, unscale, max_norm, scaler_ptr, stream))
+
+
+def gradstat_flat_noalloc(grad_ptr, dtype, n, stat_ptr, unscale=1.0, max_norm=0.0, stream=None):
+    """Statistics of one flat gradient buffer without any device allocation (see the header:
+    fixed scratch inside the library, at most ``NOALLOC_MAX_ELEMS`` elements, calls must not
+    overlap on the GPU)."""
+    check(lib().rlcu_gradstat_flat_noalloc(grad_ptr, dtype, n, unscale, max_norm, stat_ptr, stream))
