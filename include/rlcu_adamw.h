@@ -222,6 +222,74 @@ int rlcu_gradstat_finalize(rlcu_stat* stat, float unscale, float max_norm,
 int rlcu_adamw_multi_step(rlcu_tensor_list* list, const rlcu_hparams* hp,
                           const rlcu_stat* stat, uint32_t step_flags, void* stream);
 
+/* -------- ZeRO-1: optimizer state partitioned over the GPUs of one node ----- */
+/* No counterpart in RL.cu (single GPU, no NCCL).  One process (or host thread) per
+ * GPU.  All parameters live in one flat FP16 pool and all gradients in another
+ * (RL.cu's fp16_pool / half_pool layout, include/model/weights.h:43-61), both
+ * padded to rlcu_zero1_padded_elems().  The flat element space is cut into
+ * `world` equal contiguous shards; rank r keeps m / v (/ master) for shard r only.
+ * One step:
+ *   reduce-scatter (sum) of the FP16 gradients, in place       NCCL over NVLink
+ *   statistics pass on the shard, all-reduce of one double     norm over all ranks
+ *   update pass on the shard (1/world folded into the factor)
+ *   all-gather of the FP16 parameters, in place                NCCL over NVLink
+ * Result: every rank holds the parameters a single GPU would hold after a step
+ * on the mean of the ranks' gradients. */
+typedef struct rlcu_zero1 rlcu_zero1;
+
+/* One run of consecutive pool elements with the same weight decay and flags
+ * (RL.cu: projections with decay, then the embedding without, optimizer.h:125-140). */
+typedef struct rlcu_zero1_segment {
+    uint64_t n;
+    float    weight_decay;
+    uint32_t flags;            /* RLCU_TENSOR_GRAD_ZERO allowed */
+} rlcu_zero1_segment;
+
+/* What rank `rank` owns; pure host arithmetic, usable without a GPU. */
+typedef struct rlcu_zero1_plan {
+    uint64_t total;            /* sum of segment sizes                               */
+    uint64_t shard_elems;      /* ceil(total/world) rounded up to 1024               */
+    uint64_t padded_elems;     /* shard_elems * world: required pool length          */
+    uint64_t lo, hi;           /* this rank's element range, clipped to total        */
+    uint64_t pieces;           /* segments (or parts of segments) inside [lo, hi)    */
+} rlcu_zero1_plan;
+
+#define RLCU_UNIQUE_ID_BYTES 128
+int rlcu_zero1_make_plan(const rlcu_zero1_segment* segs, uint64_t nsegs, int rank, int world,
+                         rlcu_zero1_plan* out);
+/* The descriptors rank `rank` would update, with pointers expressed as element
+ * offsets from the pool / shard-state bases (param, grad: offset into the pools;
+ * m, v, master: offset into the rank's shard arrays).  `out` has room for
+ * plan.pieces entries.  Host arithmetic only. */
+int rlcu_zero1_plan_pieces(const rlcu_zero1_segment* segs, uint64_t nsegs, int rank, int world,
+                           uint64_t* pool_offset, uint64_t* state_offset, uint64_t* n,
+                           float* weight_decay, uint32_t* flags);
+/* NCCL unique id for rank 0 to hand to the other ranks (host buffer of
+ * RLCU_UNIQUE_ID_BYTES), by whatever channel the caller has. */
+int rlcu_zero1_unique_id(void* id_out);
+/* Collective over all ranks: joins the communicator and builds the shard's work
+ * table.  m_shard / v_shard / master_shard have plan.shard_elems floats
+ * (master_shard may be NULL: weights are read from the FP16 pool).  Allocates;
+ * synchronises the device. */
+int rlcu_zero1_create(const void* unique_id, int rank, int world,
+                      void* param_pool, void* grad_pool,
+                      const rlcu_zero1_segment* segs, uint64_t nsegs,
+                      float* m_shard, float* v_shard, float* master_shard,
+                      rlcu_zero1** out);
+/* One sharded optimizer step, enqueued on `stream` (no host synchronisation).
+ * `unscale` is 1/loss_scale (1 without loss scaling); the division by `world` is
+ * added inside.  `stat` is a device record that receives the global norm etc.
+ * phases: bit mask for measurements, 0 = all (1 reduce-scatter, 2 statistics +
+ * all-reduce, 4 update, 8 all-gather). */
+int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float max_norm,
+                    rlcu_scaler_state* scaler, rlcu_stat* stat, uint32_t step_flags,
+                    uint32_t phases, void* stream);
+/* Reports an asynchronous NCCL failure (a peer that died, a timed-out
+ * collective) without blocking: RLCU_OK or RLCU_ERR_NCCL. */
+int rlcu_zero1_poll_error(rlcu_zero1* z);
+/* Tears the communicator down; `abort` != 0 uses ncclCommAbort (after a failure). */
+int rlcu_zero1_destroy(rlcu_zero1* z, int abort);
+
 /* -------- host-side helpers --------------------------------------------- */
 /* 1 - powf(beta, t) in FP32 exactly as AdamWOptimizer::step (optimizer.h:121-122) */
 float rlcu_bias_correction(float beta, int step);

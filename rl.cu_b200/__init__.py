@@ -33,7 +33,11 @@ EXPORTS = [
     "rlcu_tensor_list_destroy", "rlcu_tensor_list_numel", "rlcu_tensor_list_stat_numel",
     "rlcu_tensor_list_work_items", "rlcu_gradstat", "rlcu_gradstat_finalize",
     "rlcu_adamw_multi_step", "rlcu_bias_correction", "rlcu_gradstat_flat_noalloc",
+    "rlcu_zero1_make_plan", "rlcu_zero1_plan_pieces", "rlcu_zero1_unique_id", "rlcu_zero1_create",
+    "rlcu_zero1_step", "rlcu_zero1_poll_error", "rlcu_zero1_destroy",
 ]
+UNIQUE_ID_BYTES = 128
+PHASE_REDUCE_SCATTER, PHASE_STATISTICS, PHASE_UPDATE, PHASE_ALL_GATHER = 1, 2, 4, 8
 NOALLOC_MAX_ELEMS = 1 << 31
 # C++-linkage launchers with RL.cu's signatures (include/kernels/adamw.cuh)
 CXX_EXPORTS = [
@@ -76,7 +80,19 @@ class ScalerState(C.Structure):
                 ("beta1", C.c_float), ("beta2", C.c_float), ("grad_mul", C.c_float)]
 
 
+class Zero1Segment(C.Structure):
+    """``rlcu_zero1_segment``."""
+    _fields_ = [("n", C.c_uint64), ("weight_decay", C.c_float), ("flags", C.c_uint32)]
+
+
+class Zero1Plan(C.Structure):
+    """``rlcu_zero1_plan``."""
+    _fields_ = [("total", C.c_uint64), ("shard_elems", C.c_uint64), ("padded_elems", C.c_uint64),
+                ("lo", C.c_uint64), ("hi", C.c_uint64), ("pieces", C.c_uint64)]
+
+
 assert C.sizeof(TensorDesc) == 64 and C.sizeof(Stat) == 64 and C.sizeof(ScalerState) == 32
+assert C.sizeof(Zero1Segment) == 16 and C.sizeof(Zero1Plan) == 48
 
 
 def build(force: bool = False, extra_flags: str = "") -> None:
@@ -118,6 +134,13 @@ def lib() -> C.CDLL:
     L.rlcu_gradstat_finalize.argtypes = [vp, f, f, vp, vp]
     L.rlcu_adamw_multi_step.argtypes = [vp, vp, vp, u32, vp]
     L.rlcu_gradstat_flat_noalloc.argtypes = [vp, u32, u64, f, f, vp, vp]
+    L.rlcu_zero1_make_plan.argtypes = [vp, u64, C.c_int, C.c_int, vp]
+    L.rlcu_zero1_plan_pieces.argtypes = [vp, u64, C.c_int, C.c_int, vp, vp, vp, vp, vp]
+    L.rlcu_zero1_unique_id.argtypes = [vp]
+    L.rlcu_zero1_create.argtypes = [vp, C.c_int, C.c_int, vp, vp, vp, u64, vp, vp, vp, C.POINTER(vp)]
+    L.rlcu_zero1_step.argtypes = [vp, vp, f, f, vp, vp, u32, u32, vp]
+    L.rlcu_zero1_poll_error.argtypes = [vp]
+    L.rlcu_zero1_destroy.argtypes = [vp, C.c_int]
     L.rlcu_bias_correction.argtypes = [f, C.c_int]
     L.rlcu_bias_correction.restype = f
     _lib = L
@@ -206,3 +229,75 @@ def gradstat_flat_noalloc(grad_ptr, dtype, n, stat_ptr, unscale=1.0, max_norm=0.
     fixed scratch inside the library, at most ``NOALLOC_MAX_ELEMS`` elements, calls must not
     overlap on the GPU)."""
     check(lib().rlcu_gradstat_flat_noalloc(grad_ptr, dtype, n, unscale, max_norm, stat_ptr, stream))
+
+
+# ---------------------------------------------------------------------------
+# ZeRO-1
+# ---------------------------------------------------------------------------
+
+def _segments(segments):
+    segments = list(segments)
+    arr = (Zero1Segment * max(len(segments), 1))()
+    for k, (n, wd, flags) in enumerate(segments):
+        arr[k] = Zero1Segment(n, wd, flags)
+    return arr, len(segments)
+
+
+def zero1_plan(segments, rank, world) -> Zero1Plan:
+    """Shard geometry of ``rank`` (host arithmetic; works without a GPU)."""
+    arr, n = _segments(segments)
+    plan = Zero1Plan()
+    check(lib().rlcu_zero1_make_plan(C.addressof(arr), n, rank, world, C.addressof(plan)))
+    return plan
+
+
+def zero1_pieces(segments, rank, world):
+    """[(pool_offset, state_offset, n, weight_decay, flags)] that ``rank`` updates."""
+    arr, n = _segments(segments)
+    plan = zero1_plan(segments, rank, world)
+    k = max(int(plan.pieces), 1)
+    po, so, nn = (C.c_uint64 * k)(), (C.c_uint64 * k)(), (C.c_uint64 * k)()
+    wd, fl = (C.c_float * k)(), (C.c_uint32 * k)()
+    check(lib().rlcu_zero1_plan_pieces(C.addressof(arr), n, rank, world, C.addressof(po), C.addressof(so),
+                                       C.addressof(nn), C.addressof(wd), C.addressof(fl)))
+    return [(po[i], so[i], nn[i], wd[i], fl[i]) for i in range(int(plan.pieces))]
+
+
+def zero1_unique_id() -> bytes:
+    buf = C.create_string_buffer(UNIQUE_ID_BYTES)
+    check(lib().rlcu_zero1_unique_id(buf))
+    return buf.raw
+
+
+class Zero1:
+    """Owner of an ``rlcu_zero1`` context (one per rank; creation is collective)."""
+
+    def __init__(self, unique_id: bytes, rank, world, param_pool_ptr, grad_pool_ptr, segments,
+                 m_shard_ptr, v_shard_ptr, master_shard_ptr=None):
+        arr, n = _segments(segments)
+        self.plan = zero1_plan(segments, rank, world)
+        self.rank, self.world = rank, world
+        handle = C.c_void_p()
+        idbuf = C.create_string_buffer(unique_id, UNIQUE_ID_BYTES)
+        check(lib().rlcu_zero1_create(idbuf, rank, world, param_pool_ptr, grad_pool_ptr, C.addressof(arr), n,
+                                      m_shard_ptr, v_shard_ptr, master_shard_ptr, C.byref(handle)))
+        self.handle = handle
+
+    def step(self, hp: HParams, stat_ptr, unscale=1.0, max_norm=0.0, scaler_ptr=None, step_flags=0,
+             phases=0, stream=None):
+        check(lib().rlcu_zero1_step(self.handle, C.addressof(hp), unscale, max_norm, scaler_ptr, stat_ptr,
+                                    step_flags, phases, stream))
+
+    def poll_error(self):
+        check(lib().rlcu_zero1_poll_error(self.handle))
+
+    def close(self, abort=False):
+        if self.handle:
+            h, self.handle = self.handle, C.c_void_p()
+            check(lib().rlcu_zero1_destroy(h, 1 if abort else 0))
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

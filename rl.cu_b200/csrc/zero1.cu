@@ -1,0 +1,284 @@
+// ZeRO-1 sharded optimizer step over the GPUs of one node (rlcu_zero1_* in
+// include/rlcu_adamw.h).  RL.cu has no multi-GPU code; the contract comes from
+// the step's definition: the result equals the single-GPU step on the mean of the
+// ranks' gradients.
+//
+// NCCL is bound at run time (dlopen/dlsym), not at link time: a host program that
+// has already loaded an NCCL (PyTorch bundles its own libnccl.so.2) must keep
+// using that copy, and the library must load on machines without NCCL for the
+// single-GPU entry points.
+#include "rlcu_adamw.h"
+
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <vector>
+
+#include "host_util.h"
+
+namespace {
+
+using rlcu::set_error;
+
+struct NcclApi {
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*);
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int);
+    ncclResult_t (*CommDestroy)(ncclComm_t);
+    ncclResult_t (*CommAbort)(ncclComm_t);
+    ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*);
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t);
+    ncclResult_t (*ReduceScatter)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t);
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t);
+    const char* (*GetErrorString)(ncclResult_t);
+    bool ok = false;
+};
+
+int nccl_api(const NcclApi** out) {
+    static NcclApi api;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!api.ok) {
+        void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) return set_error(RLCU_ERR_NCCL, "cannot load libnccl.so.2: %s", dlerror());
+        bool all = true;
+        auto sym = [&](const char* name) {
+            void* p = dlsym(h, name);
+            if (!p) all = false;
+            return p;
+        };
+        api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(sym("ncclGetUniqueId"));
+        api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(sym("ncclCommInitRank"));
+        api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
+        api.CommAbort = reinterpret_cast<decltype(api.CommAbort)>(sym("ncclCommAbort"));
+        api.CommGetAsyncError = reinterpret_cast<decltype(api.CommGetAsyncError)>(sym("ncclCommGetAsyncError"));
+        api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(sym("ncclAllReduce"));
+        api.ReduceScatter = reinterpret_cast<decltype(api.ReduceScatter)>(sym("ncclReduceScatter"));
+        api.AllGather = reinterpret_cast<decltype(api.AllGather)>(sym("ncclAllGather"));
+        api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
+        if (!all) return set_error(RLCU_ERR_NCCL, "libnccl.so.2 lacks a required symbol");
+        api.ok = true;
+    }
+    *out = &api;
+    return RLCU_OK;
+}
+
+#define RLCU_NCCL(api, call)                                                                  \
+    do {                                                                                      \
+        ncclResult_t rlcu_n_ = (call);                                                        \
+        if (rlcu_n_ != ncclSuccess && rlcu_n_ != ncclInProgress)                              \
+            return set_error(RLCU_ERR_NCCL, "%s: %s", #call, (api)->GetErrorString(rlcu_n_)); \
+    } while (0)
+
+constexpr uint64_t kShardAlign = 1024;   // elements: keeps every shard edge 32-byte aligned in FP32 state
+
+struct Piece {
+    uint64_t pool_offset, state_offset, n;
+    float wd;
+    uint32_t flags;
+};
+
+int check_geometry(const rlcu_zero1_segment* segs, uint64_t nsegs, int rank, int world) {
+    if (world < 1 || rank < 0 || rank >= world) return set_error(RLCU_ERR_INVALID, "rank %d of %d", rank, world);
+    if (nsegs && !segs) return set_error(RLCU_ERR_INVALID, "null segments");
+    for (uint64_t k = 0; k < nsegs; k++)
+        if (segs[k].flags & ~(uint32_t)RLCU_TENSOR_GRAD_ZERO)
+            return set_error(RLCU_ERR_INVALID, "segment %llu: unsupported flags", (unsigned long long)k);
+    return RLCU_OK;
+}
+
+void make_plan(const rlcu_zero1_segment* segs, uint64_t nsegs, int rank, int world,
+               rlcu_zero1_plan* plan, std::vector<Piece>* pieces) {
+    uint64_t total = 0;
+    for (uint64_t k = 0; k < nsegs; k++) total += segs[k].n;
+    uint64_t shard = (total + (uint64_t)world - 1) / (uint64_t)world;
+    shard = (shard + kShardAlign - 1) / kShardAlign * kShardAlign;
+    if (shard == 0) shard = kShardAlign;
+    plan->total = total;
+    plan->shard_elems = shard;
+    plan->padded_elems = shard * (uint64_t)world;
+    const uint64_t lo = shard * (uint64_t)rank;
+    const uint64_t hi = lo + shard;
+    plan->lo = lo < total ? lo : total;
+    plan->hi = hi < total ? hi : total;
+    uint64_t count = 0, begin = 0;
+    for (uint64_t k = 0; k < nsegs; k++) {
+        const uint64_t end = begin + segs[k].n;
+        const uint64_t a = begin > plan->lo ? begin : plan->lo;
+        const uint64_t b = end < plan->hi ? end : plan->hi;
+        if (a < b) {
+            count++;
+            if (pieces) pieces->push_back({a, a - lo, b - a, segs[k].weight_decay, segs[k].flags});
+        }
+        begin = end;
+    }
+    plan->pieces = count;
+}
+
+}  // namespace
+
+struct rlcu_zero1 {
+    const NcclApi* api = nullptr;
+    ncclComm_t comm = nullptr;
+    int rank = 0, world = 1;
+    rlcu_zero1_plan plan{};
+    void* param_pool = nullptr;
+    void* grad_pool = nullptr;
+    rlcu_tensor_list* list = nullptr;
+};
+
+extern "C" {
+
+int rlcu_zero1_make_plan(const rlcu_zero1_segment* segs, uint64_t nsegs, int rank, int world,
+                         rlcu_zero1_plan* out) {
+    if (!out) return set_error(RLCU_ERR_INVALID, "null plan");
+    const int rc = check_geometry(segs, nsegs, rank, world);
+    if (rc) return rc;
+    make_plan(segs, nsegs, rank, world, out, nullptr);
+    return RLCU_OK;
+}
+
+int rlcu_zero1_plan_pieces(const rlcu_zero1_segment* segs, uint64_t nsegs, int rank, int world,
+                           uint64_t* pool_offset, uint64_t* state_offset, uint64_t* n,
+                           float* weight_decay, uint32_t* flags) {
+    const int rc = check_geometry(segs, nsegs, rank, world);
+    if (rc) return rc;
+    rlcu_zero1_plan plan;
+    std::vector<Piece> pieces;
+    make_plan(segs, nsegs, rank, world, &plan, &pieces);
+    for (size_t i = 0; i < pieces.size(); i++) {
+        if (pool_offset) pool_offset[i] = pieces[i].pool_offset;
+        if (state_offset) state_offset[i] = pieces[i].state_offset;
+        if (n) n[i] = pieces[i].n;
+        if (weight_decay) weight_decay[i] = pieces[i].wd;
+        if (flags) flags[i] = pieces[i].flags;
+    }
+    return RLCU_OK;
+}
+
+int rlcu_zero1_unique_id(void* id_out) {
+    static_assert(RLCU_UNIQUE_ID_BYTES == NCCL_UNIQUE_ID_BYTES, "unique id size");
+    if (!id_out) return set_error(RLCU_ERR_INVALID, "null id buffer");
+    const NcclApi* api;
+    const int rc = nccl_api(&api);
+    if (rc) return rc;
+    RLCU_NCCL(api, api->GetUniqueId(static_cast<ncclUniqueId*>(id_out)));
+    return RLCU_OK;
+}
+
+int rlcu_zero1_create(const void* unique_id, int rank, int world,
+                      void* param_pool, void* grad_pool,
+                      const rlcu_zero1_segment* segs, uint64_t nsegs,
+                      float* m_shard, float* v_shard, float* master_shard,
+                      rlcu_zero1** out) {
+    if (!out) return set_error(RLCU_ERR_INVALID, "null out");
+    *out = nullptr;
+    if (!unique_id || !param_pool || !grad_pool || !m_shard || !v_shard)
+        return set_error(RLCU_ERR_INVALID, "null pointer");
+    int rc = check_geometry(segs, nsegs, rank, world);
+    if (rc) return rc;
+    if (reinterpret_cast<uintptr_t>(param_pool) % 16 || reinterpret_cast<uintptr_t>(grad_pool) % 16 ||
+        reinterpret_cast<uintptr_t>(m_shard) % 32 || reinterpret_cast<uintptr_t>(v_shard) % 32 ||
+        reinterpret_cast<uintptr_t>(master_shard) % 32)
+        return set_error(RLCU_ERR_INVALID, "pools must be 16-byte aligned, shard state 32-byte aligned");
+    const NcclApi* api;
+    rc = nccl_api(&api);
+    if (rc) return rc;
+
+    rlcu_zero1* z = new (std::nothrow) rlcu_zero1();
+    if (!z) return set_error(RLCU_ERR_INVALID, "out of host memory");
+    z->api = api;
+    z->rank = rank;
+    z->world = world;
+    z->param_pool = param_pool;
+    z->grad_pool = grad_pool;
+    std::vector<Piece> pieces;
+    make_plan(segs, nsegs, rank, world, &z->plan, &pieces);
+
+    std::vector<rlcu_tensor_desc> descs;
+    for (const Piece& p : pieces) {
+        rlcu_tensor_desc d{};
+        d.param = static_cast<char*>(param_pool) + p.pool_offset * 2;
+        d.grad = static_cast<const char*>(grad_pool) + p.pool_offset * 2;
+        d.m = m_shard + p.state_offset;
+        d.v = v_shard + p.state_offset;
+        d.master = master_shard ? master_shard + p.state_offset : nullptr;
+        d.n = p.n;
+        d.weight_decay = p.wd;
+        d.dtype = RLCU_F16;
+        d.flags = p.flags;
+        descs.push_back(d);
+    }
+    rc = rlcu_tensor_list_create(descs.data(), descs.size(), &z->list);
+    if (rc) {
+        delete z;
+        return rc;
+    }
+    ncclUniqueId id;
+    memcpy(&id, unique_id, sizeof(id));
+    ncclResult_t nr = api->CommInitRank(&z->comm, world, id, rank);
+    if (nr != ncclSuccess) {
+        rlcu_tensor_list_destroy(z->list);
+        delete z;
+        return set_error(RLCU_ERR_NCCL, "ncclCommInitRank: %s", api->GetErrorString(nr));
+    }
+    *out = z;
+    return RLCU_OK;
+}
+
+int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float max_norm,
+                    rlcu_scaler_state* scaler, rlcu_stat* stat, uint32_t step_flags,
+                    uint32_t phases, void* stream) {
+    if (!z || !hp || !stat) return set_error(RLCU_ERR_INVALID, "null argument");
+    if (phases == 0) phases = 15;
+    cudaStream_t s = (cudaStream_t)stream;
+    const uint64_t S = z->plan.shard_elems;
+    char* gshard = static_cast<char*>(z->grad_pool) + (uint64_t)z->rank * S * 2;
+    char* pshard = static_cast<char*>(z->param_pool) + (uint64_t)z->rank * S * 2;
+    // gradients are summed, not averaged, on the wire (FP16 would lose the small
+    // ones to the division); 1/world goes into the factor applied in registers
+    const float unscale_all = unscale / (float)z->world;
+    int rc;
+    if (phases & 1u)
+        RLCU_NCCL(z->api, z->api->ReduceScatter(z->grad_pool, gshard, S, ncclHalf, ncclSum, z->comm, s));
+    if (phases & 2u) {
+        rc = rlcu_gradstat(z->list, unscale_all, max_norm, scaler, stat, RLCU_STAT_PARTIAL, s);
+        if (rc) return rc;
+        RLCU_NCCL(z->api, z->api->AllReduce(&stat->sum_sq, &stat->sum_sq, 1, ncclDouble, ncclSum, z->comm, s));
+        rc = rlcu_gradstat_finalize(stat, unscale_all, max_norm, scaler, s);
+        if (rc) return rc;
+    }
+    if (phases & 4u) {
+        rc = rlcu_adamw_multi_step(z->list, hp, stat, step_flags, s);
+        if (rc) return rc;
+    }
+    if (phases & 8u)
+        RLCU_NCCL(z->api, z->api->AllGather(pshard, z->param_pool, S, ncclHalf, z->comm, s));
+    return RLCU_OK;
+}
+
+int rlcu_zero1_poll_error(rlcu_zero1* z) {
+    if (!z) return set_error(RLCU_ERR_INVALID, "null context");
+    ncclResult_t async = ncclSuccess;
+    RLCU_NCCL(z->api, z->api->CommGetAsyncError(z->comm, &async));
+    if (async != ncclSuccess && async != ncclInProgress)
+        return set_error(RLCU_ERR_NCCL, "asynchronous NCCL error: %s", z->api->GetErrorString(async));
+    return RLCU_OK;
+}
+
+int rlcu_zero1_destroy(rlcu_zero1* z, int abort) {
+    if (!z) return RLCU_OK;
+    int rc = RLCU_OK;
+    if (z->comm) {
+        ncclResult_t nr = abort ? z->api->CommAbort(z->comm) : z->api->CommDestroy(z->comm);
+        if (nr != ncclSuccess) rc = set_error(RLCU_ERR_NCCL, "communicator teardown: %s", z->api->GetErrorString(nr));
+    }
+    const int rc2 = rlcu_tensor_list_destroy(z->list);
+    delete z;
+    return rc ? rc : rc2;
+}
+
+}  // extern "C"

@@ -1,0 +1,155 @@
+"""ZeRO-1 sharded step on real GPUs through the C ABI (NCCL reduce-scatter / all-gather).
+
+world = 1 runs on any box.  world >= 2 spawns one process per GPU and is skipped when the
+box has fewer GPUs.  Contract: (i) the sharded update equals, bit for bit, a single-GPU step
+fed the reduce-scattered (summed) gradients with 1/world as the unscale factor; (ii) the
+reduce-scatter itself equals the FP32 sum of the replicas rounded to FP16 within 1 FP16 ulp
+per hop (exact for two ranks)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from helpers import read_stat, ulp16
+
+pytestmark = pytest.mark.gpu
+
+SEGS = [(300_000, 0.01, 0), (200_037, 0.0, 0), (8_192, 0.02, 0)]
+LR, B1, B2, EPS, T, MAX_NORM = 1e-4, 0.9, 0.999, 1e-8, 4, 1.0
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _inputs(O, world):
+    total = sum(s[0] for s in SEGS)
+    rng = np.random.default_rng(200)
+    p = O.f2h(rng.standard_normal(total).astype(np.float32) * np.float32(0.02))
+    m = (rng.standard_normal(total) * 1e-3).astype(np.float32)
+    v = (rng.random(total) * 1e-5).astype(np.float32)
+    grads = [O.f2h(np.random.default_rng([201, r]).standard_normal(total).astype(np.float32) * np.float32(5e-3))
+             for r in range(world)]
+    return total, p, m, v, grads
+
+
+def _run_rank(rank, world, uid, pkg, O, torch, use_master):
+    """Runs one sharded step on this process's GPU; returns host copies of everything."""
+    total, p, m, v, grads = _inputs(O, world)
+    plan = pkg.zero1_plan(SEGS, rank, world)
+    S, padded = int(plan.shard_elems), int(plan.padded_elems)
+    lo = rank * S
+
+    def pool16(a):
+        out = np.zeros(padded, np.uint16)
+        out[:total] = a
+        return torch.from_numpy(out.view(np.int16)).cuda()
+
+    def shard32(a):
+        out = np.zeros(padded, np.float32)
+        out[:total] = a
+        return torch.from_numpy(out[lo:lo + S].copy()).cuda()
+
+    p_pool, g_pool = pool16(p), pool16(grads[rank])
+    m_sh, v_sh = shard32(m), shard32(v)
+    master_sh = shard32(O.h2f(p)) if use_master else None
+    stat = torch.zeros(16, device="cuda")
+    z = pkg.Zero1(uid, rank, world, p_pool.data_ptr(), g_pool.data_ptr(), SEGS, m_sh.data_ptr(), v_sh.data_ptr(),
+                  master_sh.data_ptr() if use_master else None)
+    hp = pkg.hparams(LR, B1, B2, EPS, T)
+    z.step(hp, stat.data_ptr(), 1.0, MAX_NORM, None, pkg.STEP_ROUND_CLIP_FP16)
+    torch.cuda.synchronize()
+    z.poll_error()
+    out = dict(p=p_pool.cpu().numpy().view(np.uint16), g=g_pool.cpu().numpy().view(np.uint16),
+               m=m_sh.cpu().numpy(), v=v_sh.cpu().numpy(), stat=stat.cpu().numpy(), lo=lo, S=S)
+    if use_master:
+        out["master"] = master_sh.cpu().numpy()
+    z.close()
+    return out
+
+
+def _check(pkg, O, world, outs, use_master):
+    total, p, m, v, grads = _inputs(O, world)
+    S = outs[0]["S"]
+    # (ii) the reduce-scattered shard against the FP32 sum rounded once
+    exact = O.f2h(np.sum([O.h2f(g) for g in grads], axis=0, dtype=np.float32))
+    g_sum = np.zeros(total, np.uint16)
+    for r, o in enumerate(outs):
+        lo, hi = o["lo"], min(o["lo"] + S, total)
+        g_sum[lo:hi] = o["g"][lo:hi]
+    d = ulp16(g_sum, exact)
+    assert d.max() <= max(0, world - 2) + (0 if world <= 2 else 1), f"reduce-scatter off by {d.max()} ulp"
+    if world <= 2:
+        assert np.array_equal(g_sum, exact)
+    # (i) single-rank oracle step on the summed gradients, unscale = 1/world
+    master = O.h2f(p)
+    entries, off = [], 0
+    for n, wd, fl in SEGS:
+        e = dict(p=p[off:off + n], g=g_sum[off:off + n], m=m[off:off + n], v=v[off:off + n], wd=wd, flags=fl)
+        if use_master:
+            e["master"] = master[off:off + n]
+        entries.append(e)
+        off += n
+    ts = O.make_tensors(entries)
+    want = O.gradstat(ts, 1.0 / world, MAX_NORM)
+    got = pkg.Stat.from_buffer_copy(outs[0]["stat"].tobytes())
+    assert got.found_inf == 0 and got.clip_active == want.clip_active == 1
+    assert abs(got.norm - want.norm) <= 1e-5 * want.norm
+    hp = O.HParams(LR, B1, B2, EPS, O.bias_correction(B1, T), O.bias_correction(B2, T))
+    O.multi_step(ts, hp, O.gradstat_finalize(got.sum_sq, 0, 1.0 / world, MAX_NORM), O.STEP_ROUND_CLIP_FP16)
+    for r, o in enumerate(outs):
+        st = pkg.Stat.from_buffer_copy(o["stat"].tobytes())
+        assert (st.sum_sq, st.norm, st.coef) == (got.sum_sq, got.norm, got.coef), "ranks disagree on the norm"
+        assert np.array_equal(o["p"][:total], p), f"rank {r}: parameters after all-gather differ"
+        lo, hi = o["lo"], min(o["lo"] + S, total)
+        assert np.array_equal(o["m"][:hi - lo], m[lo:hi]) and np.array_equal(o["v"][:hi - lo], v[lo:hi])
+        if use_master:
+            assert np.array_equal(o["master"][:hi - lo], master[lo:hi])
+        assert not o["p"][total:].any()              # padding stays zero
+
+
+@pytest.mark.parametrize("use_master", [False, True])
+def test_world_one_equals_unsharded_step(pkg, O, use_master):
+    import torch
+    assert torch.cuda.is_available()
+    torch.cuda.set_device(0)
+    out = _run_rank(0, 1, pkg.zero1_unique_id(), pkg, O, torch, use_master)
+    _check(pkg, O, 1, [out], use_master)
+
+
+def _worker(rank, world, port, out_dir, use_master):
+    import sys
+    import torch
+    import torch.distributed as dist
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    sys.path.insert(0, os.path.join(root, "tests"))
+    import __graft_entry__ as entry
+    from oracle import oracle as O
+    pkg = entry.load_package()
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    box = [pkg.zero1_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    out = _run_rank(rank, world, box[0], pkg, O, torch, use_master)
+    np.savez(os.path.join(out_dir, f"rank{rank}.npz"), **out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharded_step_on_several_gpus(pkg, O, tmp_path, world):
+    import torch
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), world == 2), nprocs=world, join=True)
+    outs = []
+    for r in range(world):
+        z = np.load(tmp_path / f"rank{r}.npz")
+        outs.append({k: (z[k] if z[k].ndim else z[k].item()) for k in z.files})
+    _check(pkg, O, world, outs, world == 2)
