@@ -255,6 +255,16 @@ typedef struct rlcu_zero1_plan {
 } rlcu_zero1_plan;
 
 #define RLCU_UNIQUE_ID_BYTES 128
+
+/* how the two exchanges of the step are carried out */
+enum {
+    RLCU_ZERO1_NCCL = 0,  /* ncclReduceScatter / ncclAllGather around the single-GPU kernels    */
+    RLCU_ZERO1_P2P = 1    /* fused: the statistics kernel pulls every rank's gradients over
+                             NVLink through peer-mapped pointers (FP32 sum in rank order, one
+                             rounding), the update kernel pushes each new FP16 parameter into
+                             every peer's pool.  One process per GPU, pools from cudaMalloc,
+                             at most 8 ranks.  Rank ordering uses 8-byte NCCL collectives.      */
+};
 int rlcu_zero1_make_plan(const rlcu_zero1_segment* segs, uint64_t nsegs, int rank, int world,
                          rlcu_zero1_plan* out);
 /* The descriptors rank `rank` would update, with pointers expressed as element
@@ -275,12 +285,14 @@ int rlcu_zero1_create(const void* unique_id, int rank, int world,
                       void* param_pool, void* grad_pool,
                       const rlcu_zero1_segment* segs, uint64_t nsegs,
                       float* m_shard, float* v_shard, float* master_shard,
-                      rlcu_zero1** out);
+                      uint32_t mode, rlcu_zero1** out);
 /* One sharded optimizer step, enqueued on `stream` (no host synchronisation).
  * `unscale` is 1/loss_scale (1 without loss scaling); the division by `world` is
  * added inside.  `stat` is a device record that receives the global norm etc.
- * phases: bit mask for measurements, 0 = all (1 reduce-scatter, 2 statistics +
- * all-reduce, 4 update, 8 all-gather). */
+ * phases: bit mask for measurements, 0 = all.  NCCL mode: 1 reduce-scatter, 2
+ * statistics + all-reduce, 4 update, 8 all-gather.  P2P mode: 1 fused
+ * reduce-scatter + statistics, 2 all-reduce + finalize, 4 (or 8) fused update +
+ * all-gather.  RLCU_STEP_ZERO_GRADS is not available in P2P mode. */
 int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float max_norm,
                     rlcu_scaler_state* scaler, rlcu_stat* stat, uint32_t step_flags,
                     uint32_t phases, void* stream);

@@ -38,6 +38,7 @@ EXPORTS = [
 ]
 UNIQUE_ID_BYTES = 128
 PHASE_REDUCE_SCATTER, PHASE_STATISTICS, PHASE_UPDATE, PHASE_ALL_GATHER = 1, 2, 4, 8
+ZERO1_NCCL, ZERO1_P2P = 0, 1
 NOALLOC_MAX_ELEMS = 1 << 31
 # C++-linkage launchers with RL.cu's signatures (include/kernels/adamw.cuh)
 CXX_EXPORTS = [
@@ -137,7 +138,7 @@ def lib() -> C.CDLL:
     L.rlcu_zero1_make_plan.argtypes = [vp, u64, C.c_int, C.c_int, vp]
     L.rlcu_zero1_plan_pieces.argtypes = [vp, u64, C.c_int, C.c_int, vp, vp, vp, vp, vp]
     L.rlcu_zero1_unique_id.argtypes = [vp]
-    L.rlcu_zero1_create.argtypes = [vp, C.c_int, C.c_int, vp, vp, vp, u64, vp, vp, vp, C.POINTER(vp)]
+    L.rlcu_zero1_create.argtypes = [vp, C.c_int, C.c_int, vp, vp, vp, u64, vp, vp, vp, u32, C.POINTER(vp)]
     L.rlcu_zero1_step.argtypes = [vp, vp, f, f, vp, vp, u32, u32, vp]
     L.rlcu_zero1_poll_error.argtypes = [vp]
     L.rlcu_zero1_destroy.argtypes = [vp, C.c_int]
@@ -273,15 +274,16 @@ class Zero1:
     """Owner of an ``rlcu_zero1`` context (one per rank; creation is collective)."""
 
     def __init__(self, unique_id: bytes, rank, world, param_pool_ptr, grad_pool_ptr, segments,
-                 m_shard_ptr, v_shard_ptr, master_shard_ptr=None):
+                 m_shard_ptr, v_shard_ptr, master_shard_ptr=None, mode=ZERO1_NCCL):
         arr, n = _segments(segments)
         self.plan = zero1_plan(segments, rank, world)
         self.rank, self.world = rank, world
         handle = C.c_void_p()
         idbuf = C.create_string_buffer(unique_id, UNIQUE_ID_BYTES)
         check(lib().rlcu_zero1_create(idbuf, rank, world, param_pool_ptr, grad_pool_ptr, C.addressof(arr), n,
-                                      m_shard_ptr, v_shard_ptr, master_shard_ptr, C.byref(handle)))
+                                      m_shard_ptr, v_shard_ptr, master_shard_ptr, mode, C.byref(handle)))
         self.handle = handle
+        self.mode = mode
 
     def step(self, hp: HParams, stat_ptr, unscale=1.0, max_norm=0.0, scaler_ptr=None, step_flags=0,
              phases=0, stream=None):

@@ -24,215 +24,15 @@
 #include <new>
 #include <vector>
 
-#include "adamw_device.cuh"
+#include "adamw_update.cuh"
 #include "host_util.h"
+#include "tensor_list.h"
 
 namespace rlcu {
 
 // ---------------------------------------------------------------------------
 // update pass
 // ---------------------------------------------------------------------------
-
-struct GradXform {
-    float coef;        // multiply every gradient by this
-    bool round_half;   // then round FP16 gradients through binary16
-    bool zero_grads;   // write zeros over the gradient after reading it
-};
-
-template <bool ROUND>
-__device__ __forceinline__ float xform_h(float g, float coef) {
-    float x = __fmul_rn(g, coef);
-    if constexpr (ROUND) x = round_through_half(x);
-    return x;
-}
-
-// One group of 8 FP16 elements with every access vectorised.
-//   KIND 0: weight read from the FP16 parameter; KIND 1: from the FP32 master.
-template <int KIND, bool V32, bool ROUND, int U>
-__device__ __forceinline__ void f16_groups(const WorkItem& it, int first_group, int group_stride,
-                                           const StepConsts& c, float decay, const GradXform& xf) {
-    uint4 gw[U], pw[U];
-    F8 m[U], v[U], w[U];
-    const bool zero = (it.flags & RLCU_TENSOR_GRAD_ZERO) != 0;
-#pragma unroll
-    for (int u = 0; u < U; u++) {
-        const size_t e = (size_t)(first_group + u * group_stride) * kGroup;
-        gw[u] = zero ? make_uint4(0, 0, 0, 0) : ld_h8(static_cast<const __half*>(it.g) + e);
-        if constexpr (KIND == 0) pw[u] = ld_h8(static_cast<const __half*>(it.p) + e);
-        else w[u] = ld_f8<V32>(it.master + e);
-        m[u] = ld_f8<V32>(it.m + e);
-        v[u] = ld_f8<V32>(it.v + e);
-    }
-#pragma unroll
-    for (int u = 0; u < U; u++) {
-        const size_t e = (size_t)(first_group + u * group_stride) * kGroup;
-        F8 g = h8_to_f8(gw[u]);
-        if constexpr (KIND == 0) w[u] = h8_to_f8(pw[u]);
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const float x = xform_h<ROUND>(g.a[i], xf.coef);
-            w[u].a[i] = adamw_element(w[u].a[i], x, m[u].a[i], v[u].a[i], c, decay);
-        }
-        st_f8<V32>(it.m + e, m[u]);
-        st_f8<V32>(it.v + e, v[u]);
-        if constexpr (KIND == 1) st_f8<V32>(it.master + e, w[u]);
-        st_h8(static_cast<__half*>(it.p) + e, f8_to_h8(w[u]));
-        if (xf.zero_grads && !zero)
-            st_h8(const_cast<__half*>(static_cast<const __half*>(it.g)) + e, make_uint4(0, 0, 0, 0));
-    }
-}
-
-template <bool V32, int U>
-__device__ __forceinline__ void f32_groups(const WorkItem& it, int first_group, int group_stride,
-                                           const StepConsts& c, float decay, const GradXform& xf) {
-    F8 g[U], m[U], v[U], w[U];
-    const bool zero = (it.flags & RLCU_TENSOR_GRAD_ZERO) != 0;
-#pragma unroll
-    for (int u = 0; u < U; u++) {
-        const size_t e = (size_t)(first_group + u * group_stride) * kGroup;
-        if (zero) {
-#pragma unroll
-            for (int i = 0; i < 8; i++) g[u].a[i] = 0.0f;
-        } else {
-            g[u] = ld_f8<V32>(static_cast<const float*>(it.g) + e);
-        }
-        w[u] = ld_f8<V32>(static_cast<const float*>(it.p) + e);
-        m[u] = ld_f8<V32>(it.m + e);
-        v[u] = ld_f8<V32>(it.v + e);
-    }
-#pragma unroll
-    for (int u = 0; u < U; u++) {
-        const size_t e = (size_t)(first_group + u * group_stride) * kGroup;
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const float x = __fmul_rn(g[u].a[i], xf.coef);   // trainer.h:144
-            w[u].a[i] = adamw_element(w[u].a[i], x, m[u].a[i], v[u].a[i], c, decay);
-        }
-        st_f8<V32>(it.m + e, m[u]);
-        st_f8<V32>(it.v + e, v[u]);
-        st_f8<V32>(static_cast<float*>(it.p) + e, w[u]);
-        if (xf.zero_grads && !zero) {
-            F8 z;
-#pragma unroll
-            for (int i = 0; i < 8; i++) z.a[i] = 0.0f;
-            st_f8<V32>(const_cast<float*>(static_cast<const float*>(it.g)) + e, z);
-        }
-    }
-}
-
-// Element-at-a-time path: ragged tails and tensors whose pointers are not
-// 16-byte aligned.  Same arithmetic, scalar accesses.
-__device__ __forceinline__ void scalar_range(const WorkItem& it, uint32_t begin, uint32_t end,
-                                             const StepConsts& c, float decay, const GradXform& xf) {
-    const uint32_t kind = it.flags & kItemKindMask;
-    const bool zero = (it.flags & RLCU_TENSOR_GRAD_ZERO) != 0;
-    for (uint32_t i = begin + threadIdx.x; i < end; i += kThreads) {
-        float m = it.m[i], v = it.v[i];
-        if (kind == kItemKindF32) {
-            float* p = static_cast<float*>(it.p);
-            float* g = const_cast<float*>(static_cast<const float*>(it.g));
-            const float x = zero ? 0.0f : __fmul_rn(g[i], xf.coef);
-            p[i] = adamw_element(p[i], x, m, v, c, decay);
-            if (xf.zero_grads && !zero) g[i] = 0.0f;
-        } else {
-            __half* p = static_cast<__half*>(it.p);
-            __half* g = const_cast<__half*>(static_cast<const __half*>(it.g));
-            float x = zero ? 0.0f : __fmul_rn(__half2float(g[i]), xf.coef);
-            if (xf.round_half) x = round_through_half(x);
-            const float w0 = (kind == kItemKindF16Master) ? it.master[i] : __half2float(p[i]);
-            const float w = adamw_element(w0, x, m, v, c, decay);
-            if (kind == kItemKindF16Master) it.master[i] = w;
-            p[i] = __float2half_rn(w);
-            if (xf.zero_grads && !zero) g[i] = __float2half_rn(0.0f);
-        }
-        it.m[i] = m;
-        it.v[i] = v;
-    }
-}
-
-template <int KIND, bool V32, bool ROUND>
-__device__ __forceinline__ void vector_item(const WorkItem& it, const StepConsts& c, float decay,
-                                            const GradXform& xf) {
-    const int groups = it.count / kGroup;
-    if (it.count == kChunk) {
-        // full item: every thread owns kGroupsPerThread groups, loads issued two groups deep
-        constexpr int U = 2;
-#pragma unroll
-        for (int b = 0; b < kGroupsPerThread / U; b++) {
-            const int first = threadIdx.x + b * U * kThreads;
-            if constexpr (KIND == 2) f32_groups<V32, U>(it, first, kThreads, c, decay, xf);
-            else f16_groups<KIND, V32, ROUND, U>(it, first, kThreads, c, decay, xf);
-        }
-    } else {
-        for (int grp = threadIdx.x; grp < groups; grp += kThreads) {
-            if constexpr (KIND == 2) f32_groups<V32, 1>(it, grp, 0, c, decay, xf);
-            else f16_groups<KIND, V32, ROUND, 1>(it, grp, 0, c, decay, xf);
-        }
-        scalar_range(it, groups * kGroup, it.count, c, decay, xf);
-    }
-}
-
-__device__ __forceinline__ void process_item(const WorkItem& it, const StepConsts& c,
-                                             const GradXform& xf) {
-    if (it.flags & RLCU_TENSOR_NORM_ONLY) return;
-    const float decay = decay_factor(c.lr, it.wd);
-    const uint32_t kind = it.flags & kItemKindMask;
-    if (!(it.flags & kItemVec16)) {
-        scalar_range(it, 0, it.count, c, decay, xf);
-        return;
-    }
-    const bool v32 = (it.flags & kItemVec32) != 0;
-    if (kind == kItemKindF16) {
-        if (xf.round_half) {
-            if (v32) vector_item<0, true, true>(it, c, decay, xf);
-            else vector_item<0, false, true>(it, c, decay, xf);
-        } else {
-            if (v32) vector_item<0, true, false>(it, c, decay, xf);
-            else vector_item<0, false, false>(it, c, decay, xf);
-        }
-    } else if (kind == kItemKindF16Master) {
-        if (xf.round_half) {
-            if (v32) vector_item<1, true, true>(it, c, decay, xf);
-            else vector_item<1, false, true>(it, c, decay, xf);
-        } else {
-            if (v32) vector_item<1, true, false>(it, c, decay, xf);
-            else vector_item<1, false, false>(it, c, decay, xf);
-        }
-    } else {
-        if (v32) vector_item<2, true, false>(it, c, decay, xf);
-        else vector_item<2, false, false>(it, c, decay, xf);
-    }
-}
-
-__device__ __forceinline__ WorkItem load_item(const WorkItem* table, uint32_t idx) {
-    // four 16-byte loads through the read-only path; the table is re-read every
-    // step and shared by all CTAs, so it is left to the default cache policy
-    WorkItem it;
-    const uint4* src = reinterpret_cast<const uint4*>(table + idx);
-    uint4* dst = reinterpret_cast<uint4*>(&it);
-#pragma unroll
-    for (int i = 0; i < 4; i++) dst[i] = __ldg(src + i);
-    return it;
-}
-
-// Resolves the per-launch constants from the statistics record (if any).
-// Returns false when the step must be skipped.
-__device__ __forceinline__ bool resolve_step(const rlcu_stat* stat, uint32_t step_flags,
-                                             StepConsts& c, GradXform& xf) {
-    xf.coef = 1.0f;
-    xf.round_half = false;
-    xf.zero_grads = (step_flags & RLCU_STEP_ZERO_GRADS) != 0;
-    if (stat) {
-        if (stat->found_inf) return false;
-        xf.coef = stat->coef;
-        xf.round_half = (step_flags & RLCU_STEP_ROUND_CLIP_FP16) && stat->clip_active;
-        if (step_flags & RLCU_STEP_DEVICE_BIAS_CORRECTION) {
-            c.bc1_inv = __fdiv_rn(1.0f, stat->bias_correction1);
-            c.bc2_inv = __fdiv_rn(1.0f, stat->bias_correction2);
-        }
-    }
-    return true;
-}
 
 // Multi-tensor update: persistent CTAs walk the work table with a grid stride.
 __global__ void __launch_bounds__(kThreads)
@@ -263,7 +63,7 @@ adamw_table_kernel(const WorkItem* __restrict__ table, uint32_t n_items, StepCon
         const WorkItem it = next;
         const uint32_t nidx = idx + gridDim.x;
         if (nidx < n_items) next = load_item(table, nidx);   // fetched under the data loads
-        process_item(it, c, xf);
+        process_item<false>(it, c, xf, PeerOut{});
         if (nidx >= n_items) break;
         idx = nidx;
     }
@@ -293,7 +93,7 @@ adamw_flat_kernel(WorkItem base, uint64_t n, StepConsts c) {
             it.p = static_cast<__half*>(base.p) + off;
             it.g = static_cast<const __half*>(base.g) + off;
         }
-        process_item(it, c, xf);
+        process_item<false>(it, c, xf, PeerOut{});
     }
 }
 
@@ -488,18 +288,6 @@ __global__ void finalize_kernel(rlcu_stat* stat, float unscale_arg, float max_no
 // ===========================================================================
 
 using namespace rlcu;
-
-struct rlcu_tensor_list {
-    int device = -1;
-    WorkItem* d_items = nullptr;
-    uint32_t n_items = 0;
-    uint64_t numel = 0;        // elements the update pass touches
-    uint64_t stat_numel = 0;   // elements the statistics pass reads
-    float* d_partials = nullptr;
-    unsigned int* d_counter = nullptr;
-    int grid_update = 0;
-    int grid_stat = 0;
-};
 
 namespace {
 

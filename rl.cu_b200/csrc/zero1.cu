@@ -18,6 +18,7 @@
 #include <vector>
 
 #include "host_util.h"
+#include "zero1_p2p.h"
 
 namespace {
 
@@ -124,11 +125,140 @@ struct rlcu_zero1 {
     const NcclApi* api = nullptr;
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1;
+    uint32_t mode = RLCU_ZERO1_NCCL;
     rlcu_zero1_plan plan{};
     void* param_pool = nullptr;
     void* grad_pool = nullptr;
     rlcu_tensor_list* list = nullptr;
+    // peer-to-peer mode: the other ranks' pools mapped into this process
+    int* d_barrier = nullptr;
+    rlcu::PeerIn grads_in{};
+    rlcu::PeerOut params_out{};
+    std::vector<void*> mapped;     // what cudaIpcOpenMemHandle returned, to be closed
 };
+
+namespace {
+
+// what each rank tells the others about its two pools
+struct PoolExport {
+    cudaIpcMemHandle_t grad_handle, param_handle;
+    uint64_t grad_offset, param_offset;     // of the pool inside its allocation
+    int32_t ok, pad;
+};
+
+// base address of the allocation that contains `ptr` (the IPC handle names the
+// whole allocation, and callers hand in pointers carved out of larger blocks)
+int allocation_base(const void* ptr, void** base) {
+    typedef int (*GetRange)(unsigned long long*, size_t*, unsigned long long);
+    static GetRange fn = nullptr;
+    if (!fn) {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        RLCU_CUDA(cudaGetDriverEntryPoint("cuMemGetAddressRange", &f, cudaEnableDefault, &qr));
+        if (!f || qr != cudaDriverEntryPointSuccess)
+            return set_error(RLCU_ERR_CUDA, "cuMemGetAddressRange is not available");
+        fn = reinterpret_cast<GetRange>(f);
+    }
+    unsigned long long b = 0;
+    size_t size = 0;
+    if (fn(&b, &size, (unsigned long long)reinterpret_cast<uintptr_t>(ptr)) != 0)
+        return set_error(RLCU_ERR_CUDA, "cuMemGetAddressRange failed for %p", ptr);
+    *base = reinterpret_cast<void*>((uintptr_t)b);
+    return RLCU_OK;
+}
+
+int barrier(rlcu_zero1* z, cudaStream_t s) {
+    RLCU_NCCL(z->api, z->api->AllReduce(z->d_barrier, z->d_barrier, 1, ncclInt32, ncclSum, z->comm, s));
+    return RLCU_OK;
+}
+
+// Maps every peer's gradient and parameter pool into this process.  Collective.
+int setup_p2p(rlcu_zero1* z) {
+    const int W = z->world;
+    if (W > rlcu::kMaxWorld) return set_error(RLCU_ERR_UNSUPPORTED, "peer-to-peer mode supports at most %d ranks", rlcu::kMaxWorld);
+    RLCU_CUDA(cudaMalloc(&z->d_barrier, 256));
+    RLCU_CUDA(cudaMemset(z->d_barrier, 0, 256));
+
+    PoolExport mine{};
+    void *gbase = nullptr, *pbase = nullptr;
+    int rc = allocation_base(z->grad_pool, &gbase);
+    if (!rc) rc = allocation_base(z->param_pool, &pbase);
+    bool ok = rc == RLCU_OK;
+    if (ok && W > 1) {
+        ok = cudaIpcGetMemHandle(&mine.grad_handle, gbase) == cudaSuccess &&
+             cudaIpcGetMemHandle(&mine.param_handle, pbase) == cudaSuccess;
+        if (!ok) set_error(RLCU_ERR_CUDA, "cudaIpcGetMemHandle failed (pools must come from cudaMalloc): %s",
+                           cudaGetErrorString(cudaGetLastError()));
+    }
+    mine.grad_offset = ok ? (uint64_t)((char*)z->grad_pool - (char*)gbase) : 0;
+    mine.param_offset = ok ? (uint64_t)((char*)z->param_pool - (char*)pbase) : 0;
+    mine.ok = ok ? 1 : 0;
+
+    std::vector<PoolExport> all(W);
+    PoolExport* d_all = nullptr;
+    RLCU_CUDA(cudaMalloc(&d_all, sizeof(PoolExport) * W));
+    RLCU_CUDA(cudaMemcpy(d_all + z->rank, &mine, sizeof(PoolExport), cudaMemcpyHostToDevice));
+    ncclResult_t nr = z->api->AllGather(d_all + z->rank, d_all, sizeof(PoolExport), ncclInt8, z->comm, 0);
+    cudaError_t ce = cudaStreamSynchronize(0);
+    if (nr == ncclSuccess && ce == cudaSuccess)
+        ce = cudaMemcpy(all.data(), d_all, sizeof(PoolExport) * W, cudaMemcpyDeviceToHost);
+    cudaFree(d_all);
+    if (nr != ncclSuccess) return set_error(RLCU_ERR_NCCL, "handle exchange: %s", z->api->GetErrorString(nr));
+    if (ce != cudaSuccess) return set_error(RLCU_ERR_CUDA, "handle exchange: %s", cudaGetErrorString(ce));
+    for (int j = 0; j < W; j++)
+        if (!all[j].ok) return ok ? set_error(RLCU_ERR_CUDA, "rank %d could not export its pools", j) : RLCU_ERR_CUDA;
+
+    z->grads_in.n = W;
+    z->grads_in.local_base = static_cast<const __half*>(z->grad_pool);
+    z->params_out.n = 0;
+    z->params_out.local_base = static_cast<const __half*>(z->param_pool);
+    bool opened_all = true;
+    for (int j = 0; j < W && opened_all; j++) {
+        if (j == z->rank) {
+            z->grads_in.base[j] = static_cast<const __half*>(z->grad_pool);
+            continue;
+        }
+        void *g = nullptr, *p = nullptr;
+        if (cudaIpcOpenMemHandle(&g, all[j].grad_handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            set_error(RLCU_ERR_CUDA, "cudaIpcOpenMemHandle(rank %d gradients): %s", j, cudaGetErrorString(cudaGetLastError()));
+            opened_all = false;
+            break;
+        }
+        z->mapped.push_back(g);
+        if (memcmp(&all[j].grad_handle, &all[j].param_handle, sizeof(cudaIpcMemHandle_t)) == 0) {
+            p = g;                      // both pools live in one allocation
+        } else if (cudaIpcOpenMemHandle(&p, all[j].param_handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            set_error(RLCU_ERR_CUDA, "cudaIpcOpenMemHandle(rank %d parameters): %s", j, cudaGetErrorString(cudaGetLastError()));
+            opened_all = false;
+            break;
+        } else {
+            z->mapped.push_back(p);
+        }
+        z->grads_in.base[j] = reinterpret_cast<const __half*>((char*)g + all[j].grad_offset);
+        z->params_out.base[z->params_out.n++] = reinterpret_cast<__half*>((char*)p + all[j].param_offset);
+    }
+    // every rank must agree that the mapping worked before anyone relies on it
+    int flag = opened_all ? 0 : 1;
+    RLCU_CUDA(cudaMemcpy(z->d_barrier, &flag, sizeof(int), cudaMemcpyHostToDevice));
+    nr = z->api->AllReduce(z->d_barrier, z->d_barrier, 1, ncclInt32, ncclSum, z->comm, 0);
+    ce = cudaStreamSynchronize(0);
+    int failed = 1;
+    if (nr == ncclSuccess && ce == cudaSuccess) ce = cudaMemcpy(&failed, z->d_barrier, sizeof(int), cudaMemcpyDeviceToHost);
+    cudaMemset(z->d_barrier, 0, 256);
+    if (nr != ncclSuccess) return set_error(RLCU_ERR_NCCL, "mapping agreement: %s", z->api->GetErrorString(nr));
+    if (ce != cudaSuccess) return set_error(RLCU_ERR_CUDA, "mapping agreement: %s", cudaGetErrorString(ce));
+    if (failed) return opened_all ? set_error(RLCU_ERR_CUDA, "another rank could not map the pools") : RLCU_ERR_CUDA;
+    return RLCU_OK;
+}
+
+void release_p2p(rlcu_zero1* z) {
+    for (void* p : z->mapped) cudaIpcCloseMemHandle(p);
+    z->mapped.clear();
+    if (z->d_barrier) cudaFree(z->d_barrier);
+    z->d_barrier = nullptr;
+}
+
+}  // namespace
 
 extern "C" {
 
@@ -173,8 +303,9 @@ int rlcu_zero1_create(const void* unique_id, int rank, int world,
                       void* param_pool, void* grad_pool,
                       const rlcu_zero1_segment* segs, uint64_t nsegs,
                       float* m_shard, float* v_shard, float* master_shard,
-                      rlcu_zero1** out) {
+                      uint32_t mode, rlcu_zero1** out) {
     if (!out) return set_error(RLCU_ERR_INVALID, "null out");
+    if (mode != RLCU_ZERO1_NCCL && mode != RLCU_ZERO1_P2P) return set_error(RLCU_ERR_INVALID, "unknown mode %u", mode);
     *out = nullptr;
     if (!unique_id || !param_pool || !grad_pool || !m_shard || !v_shard)
         return set_error(RLCU_ERR_INVALID, "null pointer");
@@ -193,6 +324,7 @@ int rlcu_zero1_create(const void* unique_id, int rank, int world,
     z->api = api;
     z->rank = rank;
     z->world = world;
+    z->mode = mode;
     z->param_pool = param_pool;
     z->grad_pool = grad_pool;
     std::vector<Piece> pieces;
@@ -225,6 +357,16 @@ int rlcu_zero1_create(const void* unique_id, int rank, int world,
         delete z;
         return set_error(RLCU_ERR_NCCL, "ncclCommInitRank: %s", api->GetErrorString(nr));
     }
+    if (mode == RLCU_ZERO1_P2P) {
+        rc = setup_p2p(z);
+        if (rc) {
+            release_p2p(z);
+            api->CommAbort(z->comm);
+            rlcu_tensor_list_destroy(z->list);
+            delete z;
+            return rc;
+        }
+    }
     *out = z;
     return RLCU_OK;
 }
@@ -242,6 +384,31 @@ int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float 
     // ones to the division); 1/world goes into the factor applied in registers
     const float unscale_all = unscale / (float)z->world;
     int rc;
+    if (z->mode == RLCU_ZERO1_P2P) {
+        if (step_flags & RLCU_STEP_ZERO_GRADS)
+            return set_error(RLCU_ERR_UNSUPPORTED, "RLCU_STEP_ZERO_GRADS is not available in the sharded step");
+        if (phases & 1u) {
+            // every rank's gradients are complete before anyone reads them remotely
+            rc = barrier(z, s);
+            if (rc) return rc;
+            rc = rlcu::launch_reduce_stat(z->list, z->grads_in, unscale_all, scaler, stat, s);
+            if (rc) return rc;
+        }
+        if (phases & 2u) {
+            // the sum over ranks doubles as "all remote reads of my gradients are done"
+            RLCU_NCCL(z->api, z->api->AllReduce(&stat->sum_sq, &stat->sum_sq, 1, ncclDouble, ncclSum, z->comm, s));
+            rc = rlcu_gradstat_finalize(stat, unscale_all, max_norm, scaler, s);
+            if (rc) return rc;
+        }
+        if (phases & (4u | 8u)) {
+            rc = rlcu::launch_update_peers(z->list, hp, stat, step_flags, z->params_out, s);
+            if (rc) return rc;
+            // every rank's stores into my pool have landed before I use the parameters
+            rc = barrier(z, s);
+            if (rc) return rc;
+        }
+        return RLCU_OK;
+    }
     if (phases & 1u)
         RLCU_NCCL(z->api, z->api->ReduceScatter(z->grad_pool, gshard, S, ncclHalf, ncclSum, z->comm, s));
     if (phases & 2u) {
@@ -276,6 +443,7 @@ int rlcu_zero1_destroy(rlcu_zero1* z, int abort) {
         ncclResult_t nr = abort ? z->api->CommAbort(z->comm) : z->api->CommDestroy(z->comm);
         if (nr != ncclSuccess) rc = set_error(RLCU_ERR_NCCL, "communicator teardown: %s", z->api->GetErrorString(nr));
     }
+    release_p2p(z);
     const int rc2 = rlcu_tensor_list_destroy(z->list);
     delete z;
     return rc ? rc : rc2;
