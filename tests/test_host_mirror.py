@@ -1,0 +1,52 @@
+"""The C++ AdamWOptimizer mirror (include/training/optimizer.h).
+
+CPU: it compiles against a stand-in for RL.cu's model header, and -- when a checkout of RL.cu
+sits at RLCU_REFERENCE (default /root/reference) -- RL.cu's own tests/test_adamw.cu compiles
+unchanged against it.  GPU: the mirror's test program runs and reports no failure."""
+import os
+import shutil
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CPP = os.path.join(ROOT, "tests", "cpp")
+REF = os.environ.get("RLCU_REFERENCE", "/root/reference")
+NVCC = ["nvcc", "-std=c++17", "-O2", "--expt-relaxed-constexpr", "-gencode", "arch=compute_100a,code=sm_100a"]
+
+
+@pytest.fixture(scope="module")
+def mirror_binary(pkg, tmp_path_factory):
+    if shutil.which("nvcc") is None:
+        pytest.skip("nvcc not available")
+    out = str(tmp_path_factory.mktemp("mirror") / "test_optimizer_mirror")
+    lib_dir = os.path.join(ROOT, "rl.cu_b200", "lib")
+    cmd = NVCC + ["-I", os.path.join(ROOT, "include"), "-I", os.path.join(CPP, "stub"),
+                  os.path.join(CPP, "test_optimizer_mirror.cu"), "-o", out,
+                  "-L", lib_dir, "-lrlcu_b200", "-Xlinker", f"-rpath={lib_dir}"]
+    subprocess.run(cmd, check=True)
+    return out
+
+
+def test_mirror_builds_against_the_stand_in_model_header(mirror_binary):
+    assert os.path.exists(mirror_binary)
+
+
+def test_reference_test_source_compiles_against_the_mirror(tmp_path):
+    """RL.cu's tests/test_adamw.cu, unchanged, with this repository's include/ first."""
+    src = os.path.join(REF, "tests", "test_adamw.cu")
+    if not os.path.exists(src) or shutil.which("nvcc") is None:
+        pytest.skip("no checkout of RL.cu here")
+    cmd = NVCC + ["-I", os.path.join(ROOT, "include"), "-I", os.path.join(REF, "include"),
+                  "-c", src, "-o", str(tmp_path / "test_adamw.o")]
+    subprocess.run(cmd, check=True)
+    syms = subprocess.run(["nm", "-C", str(tmp_path / "test_adamw.o")], check=True, capture_output=True, text=True).stdout
+    assert "rlcu_adamw_multi_step" in syms          # the mirror, not RL.cu's header, was picked up
+
+
+@pytest.mark.gpu
+def test_mirror_program_passes_on_the_gpu(mirror_binary):
+    r = subprocess.run([mirror_binary], capture_output=True, text=True)
+    print(r.stdout)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "[FAIL]" not in r.stdout and r.stdout.count("[PASS]") >= 13
