@@ -59,6 +59,11 @@ def shapes_for(workload):
     if workload == "qwen3-0.6b-4l":     # 4 of the 28 layers + embedding: the profiler-sized case
         from helpers import qwen3_shapes
         return qwen3_shapes(1024, 3072, 4, 151936, 16, 8, 128, tied=True)
+    if workload == "ragged-20k":        # 20,000 tensors, sizes log-uniform in [64, 4,194,304], seed 0
+        import numpy as np
+        rng = np.random.default_rng(0)
+        sizes = np.floor(np.exp(rng.uniform(np.log(64), np.log(4_194_304), 20_000))).astype(np.int64)
+        return [(f"t{k}", int(n), True) for k, n in enumerate(sizes)]
     raise SystemExit(f"unknown workload {workload}")
 
 
@@ -119,9 +124,11 @@ class ClockSampler:
 
 
 def build_pools(torch, shapes, dev, seed):
-    """Flat pools in RL.cu's order with one descriptor per tensor.  FP16 params ~N(0,0.02)
-    with norm weights 1.0, FP16 grads ~N(0,1e-4), FP32 moments zero."""
-    total = sum(n for _, n, _ in shapes)
+    """Flat pools in RL.cu's order with one descriptor per tensor, every tensor starting on a
+    16-byte boundary (a no-op for the Qwen3 shapes, padding for ragged ones).  FP16 params
+    ~N(0,0.02) with norm weights 1.0, FP16 grads ~N(0,1e-4), FP32 moments zero."""
+    params = sum(n for _, n, _ in shapes)
+    total = sum((n + 7) // 8 * 8 for _, n, _ in shapes)
     gen = torch.Generator(device=dev).manual_seed(seed)
     p = torch.empty(total, dtype=torch.float16, device=dev)
     g = torch.empty(total, dtype=torch.float16, device=dev)
@@ -134,10 +141,10 @@ def build_pools(torch, shapes, dev, seed):
     for name, n, _ in shapes:
         if "norm" in name:
             p[off:off + n] = 1.0
-        off += n
+        off += (n + 7) // 8 * 8
     m = torch.zeros(total, dtype=torch.float32, device=dev)
     v = torch.zeros(total, dtype=torch.float32, device=dev)
-    return dict(p=p, g=g, m=m, v=v, total=total)
+    return dict(p=p, g=g, m=m, v=v, total=params, arena=total)
 
 
 def fresh_grads(torch, g, gen):
@@ -153,7 +160,7 @@ def make_descs(pkg, pools, shapes, wd):
         descs.append(pkg.TensorDesc(pools["p"].data_ptr() + 2 * off, pools["g"].data_ptr() + 2 * off,
                                     pools["m"].data_ptr() + 4 * off, pools["v"].data_ptr() + 4 * off,
                                     None, n, wd if decays else 0.0, pkg.F16, 0, 0))
-        off += n
+        off += (n + 7) // 8 * 8
     return descs
 
 
@@ -206,7 +213,8 @@ def run_reference_arm(args):
 
 
 def workload_name(args):
-    base = {"qwen3-0.6b-4l": "Qwen3-0.6B shapes cut to 4 layers + embedding (profiling case), clip 1.0",
+    base = {"ragged-20k": "20,000 FP16 tensors with log-uniform sizes in [64, 4,194,304] (7,544,329,889 params), clip 1.0",
+            "qwen3-0.6b-4l": "Qwen3-0.6B shapes cut to 4 layers + embedding (profiling case), clip 1.0",
             "qwen3-0.6b": "Qwen3-0.6B-shaped multi-tensor AdamW step, 596,049,920 params in 310 tensors, clip 1.0",
             "qwen3-8b": "Qwen3-8B-shaped multi-tensor AdamW step, 8,190,735,360 params in 399 tensors, clip 1.0"}[args.workload]
     if args.gpus > 1:
@@ -280,7 +288,7 @@ def run_single(args):
         return
 
     # ---- end to end from host memory: H2D of the step's gradients, step, D2H of the record
-    host_g = torch.empty(P, dtype=torch.float16).pin_memory()
+    host_g = torch.empty(pools["g"].numel(), dtype=torch.float16).pin_memory()
     host_g.copy_(pools["g"])
     host_stat = torch.empty(16, dtype=torch.float32).pin_memory()
     e2e_steps = max(3, min(K, 20))
@@ -573,7 +581,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="qwen3-0.6b", choices=["qwen3-0.6b", "qwen3-8b", "qwen3-0.6b-4l"])
+    ap.add_argument("--workload", default="qwen3-0.6b", choices=["qwen3-0.6b", "qwen3-8b", "qwen3-0.6b-4l", "ragged-20k"])
     ap.add_argument("--zero1-mode", default="p2p", choices=["p2p", "nccl"],
                     help="N>1: fused peer-to-peer kernels (default) or NCCL reduce-scatter/all-gather")
     ap.add_argument("--quick", action="store_true",
