@@ -8,10 +8,24 @@
 
 namespace rlcu {
 
+// Tuning knobs (the defaults are the measured best on B200; the macros exist so that
+// variants can be built side by side and timed).
+#ifndef RLCU_CHUNK
+#define RLCU_CHUNK 8192
+#endif
+#ifndef RLCU_UNROLL
+#define RLCU_UNROLL 2
+#endif
+#ifndef RLCU_POLICY
+#define RLCU_POLICY 0      // 0 streaming (.cs), 1 default, 2 L1::no_allocate + L2::evict_first loads
+#endif
+
 constexpr int kThreads = 256;          // threads per CTA for every kernel here
 constexpr int kGroup = 8;              // elements one thread moves per access set
-constexpr int kChunk = 8192;           // elements per work item (= 4 groups per thread)
+constexpr int kChunk = RLCU_CHUNK;     // elements per work item (= 4 groups per thread)
 constexpr int kGroupsPerThread = kChunk / (kThreads * kGroup);
+constexpr int kUnroll = RLCU_UNROLL;   // groups whose loads are issued before any arithmetic
+static_assert(kChunk % (kThreads * kGroup) == 0 && kGroupsPerThread % kUnroll == 0, "chunk geometry");
 
 // Internal per-item bits kept above the public RLCU_TENSOR_* flags.
 constexpr uint32_t kItemKindMask = 0x3u << 8;   // 0 F16, 1 F16+master, 2 F32
@@ -55,7 +69,13 @@ template <bool V32>
 __device__ __forceinline__ F8 ld_f8(const float* p) {
     F8 r;
     if constexpr (V32) {
+#if RLCU_POLICY == 1
+        asm volatile("ld.global.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+#elif RLCU_POLICY == 2
+        asm volatile("ld.global.L1::no_allocate.L2::evict_first.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+#else
         asm volatile("ld.global.cs.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+#endif
                      : "=f"(r.a[0]), "=f"(r.a[1]), "=f"(r.a[2]), "=f"(r.a[3]),
                        "=f"(r.a[4]), "=f"(r.a[5]), "=f"(r.a[6]), "=f"(r.a[7])
                      : "l"(p));
@@ -71,7 +91,11 @@ __device__ __forceinline__ F8 ld_f8(const float* p) {
 template <bool V32>
 __device__ __forceinline__ void st_f8(float* p, const F8& r) {
     if constexpr (V32) {
+#if RLCU_POLICY == 1
+        asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+#else
         asm volatile("st.global.cs.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+#endif
                      :: "l"(p), "f"(r.a[0]), "f"(r.a[1]), "f"(r.a[2]), "f"(r.a[3]),
                         "f"(r.a[4]), "f"(r.a[5]), "f"(r.a[6]), "f"(r.a[7])
                      : "memory");
@@ -82,11 +106,19 @@ __device__ __forceinline__ void st_f8(float* p, const F8& r) {
 }
 
 __device__ __forceinline__ uint4 ld_h8(const void* p) {
+#if RLCU_POLICY == 1
+    return *reinterpret_cast<const uint4*>(p);
+#else
     return __ldcs(reinterpret_cast<const uint4*>(p));
+#endif
 }
 
 __device__ __forceinline__ void st_h8(void* p, uint4 x) {
+#if RLCU_POLICY == 1
+    *reinterpret_cast<uint4*>(p) = x;
+#else
     __stcs(reinterpret_cast<uint4*>(p), x);
+#endif
 }
 
 __device__ __forceinline__ F8 h8_to_f8(uint4 x) {

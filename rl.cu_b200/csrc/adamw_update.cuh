@@ -161,8 +161,8 @@ __device__ __forceinline__ void vector_item(const WorkItem& it, const StepConsts
                                             const GradXform& xf, const PeerOut& peers) {
     const int groups = it.count / kGroup;
     if (it.count == kChunk) {
-        // full item: every thread owns kGroupsPerThread groups, loads issued two groups deep
-        constexpr int U = 2;
+        // full item: every thread owns kGroupsPerThread groups, loads issued kUnroll groups deep
+        constexpr int U = kUnroll;
 #pragma unroll
         for (int b = 0; b < kGroupsPerThread / U; b++) {
             const int first = threadIdx.x + b * U * kThreads;

@@ -35,7 +35,11 @@ namespace rlcu {
 // ---------------------------------------------------------------------------
 
 // Multi-tensor update: persistent CTAs walk the work table with a grid stride.
+#ifdef RLCU_MIN_CTAS
+__global__ void __launch_bounds__(kThreads, RLCU_MIN_CTAS)
+#else
 __global__ void __launch_bounds__(kThreads)
+#endif
 adamw_table_kernel(const WorkItem* __restrict__ table, uint32_t n_items, StepConsts c,
                    const rlcu_stat* __restrict__ stat, uint32_t step_flags) {
     GradXform xf;
