@@ -59,10 +59,11 @@ def shapes_for(workload):
     if workload == "qwen3-0.6b-4l":     # 4 of the 28 layers + embedding: the profiler-sized case
         from helpers import qwen3_shapes
         return qwen3_shapes(1024, 3072, 4, 151936, 16, 8, 128, tied=True)
-    if workload == "ragged-20k":        # 20,000 tensors, sizes log-uniform in [64, 4,194,304], seed 0
+    if workload in ("ragged-20k", "ragged-600"):   # sizes log-uniform in [64, 4,194,304], seed 0
         import numpy as np
         rng = np.random.default_rng(0)
-        sizes = np.floor(np.exp(rng.uniform(np.log(64), np.log(4_194_304), 20_000))).astype(np.int64)
+        count = 20_000 if workload == "ragged-20k" else 600        # 600: the profiler-sized cut
+        sizes = np.floor(np.exp(rng.uniform(np.log(64), np.log(4_194_304), count))).astype(np.int64)
         return [(f"t{k}", int(n), True) for k, n in enumerate(sizes)]
     raise SystemExit(f"unknown workload {workload}")
 
@@ -123,12 +124,13 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
-def build_pools(torch, shapes, dev, seed):
+def build_pools(torch, shapes, dev, seed, align=8):
     """Flat pools in RL.cu's order with one descriptor per tensor, every tensor starting on a
     16-byte boundary (a no-op for the Qwen3 shapes, padding for ragged ones).  FP16 params
     ~N(0,0.02) with norm weights 1.0, FP16 grads ~N(0,1e-4), FP32 moments zero."""
     params = sum(n for _, n, _ in shapes)
-    total = sum((n + 7) // 8 * 8 for _, n, _ in shapes)
+    pad = lambda n: (n + align - 1) // align * align
+    total = sum(pad(n) for _, n, _ in shapes)
     gen = torch.Generator(device=dev).manual_seed(seed)
     p = torch.empty(total, dtype=torch.float16, device=dev)
     g = torch.empty(total, dtype=torch.float16, device=dev)
@@ -141,7 +143,7 @@ def build_pools(torch, shapes, dev, seed):
     for name, n, _ in shapes:
         if "norm" in name:
             p[off:off + n] = 1.0
-        off += (n + 7) // 8 * 8
+        off += pad(n)
     m = torch.zeros(total, dtype=torch.float32, device=dev)
     v = torch.zeros(total, dtype=torch.float32, device=dev)
     return dict(p=p, g=g, m=m, v=v, total=params, arena=total)
@@ -154,13 +156,13 @@ def fresh_grads(torch, g, gen):
         g[lo:hi] = (torch.randn(hi - lo, device=g.device, generator=gen) * 1e-4).half()
 
 
-def make_descs(pkg, pools, shapes, wd):
+def make_descs(pkg, pools, shapes, wd, align=8):
     descs, off = [], 0
     for _, n, decays in shapes:
         descs.append(pkg.TensorDesc(pools["p"].data_ptr() + 2 * off, pools["g"].data_ptr() + 2 * off,
                                     pools["m"].data_ptr() + 4 * off, pools["v"].data_ptr() + 4 * off,
                                     None, n, wd if decays else 0.0, pkg.F16, 0, 0))
-        off += (n + 7) // 8 * 8
+        off += (n + align - 1) // align * align
     return descs
 
 
@@ -213,7 +215,8 @@ def run_reference_arm(args):
 
 
 def workload_name(args):
-    base = {"ragged-20k": "20,000 FP16 tensors with log-uniform sizes in [64, 4,194,304] (7,544,329,889 params), clip 1.0",
+    base = {"ragged-600": "600 FP16 tensors with log-uniform sizes in [64, 4,194,304] (profiling cut of ragged-20k), clip 1.0",
+            "ragged-20k": "20,000 FP16 tensors with log-uniform sizes in [64, 4,194,304] (7,544,329,889 params), clip 1.0",
             "qwen3-0.6b-4l": "Qwen3-0.6B shapes cut to 4 layers + embedding (profiling case), clip 1.0",
             "qwen3-0.6b": "Qwen3-0.6B-shaped multi-tensor AdamW step, 596,049,920 params in 310 tensors, clip 1.0",
             "qwen3-8b": "Qwen3-8B-shaped multi-tensor AdamW step, 8,190,735,360 params in 399 tensors, clip 1.0"}[args.workload]
@@ -235,10 +238,10 @@ def run_single(args):
     torch.cuda.set_device(0)
     dev = torch.device("cuda:0")
     shapes = shapes_for(args.workload)
-    pools = build_pools(torch, shapes, dev, seed=0)
+    pools = build_pools(torch, shapes, dev, seed=0, align=args.align)
     P = pools["total"]
     lr, b1, b2, eps, wd, max_norm = 1e-6, 0.9, 0.999, 1e-8, 0.01, 1.0
-    tl = pkg.TensorList(make_descs(pkg, pools, shapes, wd))
+    tl = pkg.TensorList(make_descs(pkg, pools, shapes, wd, align=args.align))
     stat = torch.zeros(16, dtype=torch.float32, device=dev)
     stream = torch.cuda.current_stream().cuda_stream
     flags = pkg.STEP_ROUND_CLIP_FP16
@@ -581,9 +584,11 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="qwen3-0.6b", choices=["qwen3-0.6b", "qwen3-8b", "qwen3-0.6b-4l", "ragged-20k"])
+    ap.add_argument("--workload", default="qwen3-0.6b", choices=["qwen3-0.6b", "qwen3-8b", "qwen3-0.6b-4l", "ragged-20k", "ragged-600"])
     ap.add_argument("--zero1-mode", default="p2p", choices=["p2p", "nccl"],
                     help="N>1: fused peer-to-peer kernels (default) or NCCL reduce-scatter/all-gather")
+    ap.add_argument("--align", type=int, default=8,
+                    help="N=1: elements every tensor start is aligned to inside the pools (8 = 16 bytes)")
     ap.add_argument("--quick", action="store_true",
                     help="device-resident timing only (no end-to-end, CPU or reference-kernel legs): for profiler runs")
     args = ap.parse_args()

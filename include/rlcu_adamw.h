@@ -302,6 +302,33 @@ int rlcu_zero1_poll_error(rlcu_zero1* z);
 /* Tears the communicator down; `abort` != 0 uses ncclCommAbort (after a failure). */
 int rlcu_zero1_destroy(rlcu_zero1* z, int abort);
 
+/* -------- optimizer-state checkpoint ------------------------------------- */
+/* RL.cu's Trainer::save_checkpoint is a stub (include/training/trainer.h:317-319;
+ * the configuration already carries save_dir / save_steps, trainer.h:35, 47-48).
+ * One file per rank holds what is needed to continue bit-identically: the Adam
+ * step counter, the loss-scale state and the rank's m / v (/ master) arrays.
+ * Layout: 128-byte little-endian header, then m, v, master as raw FP32, then a
+ * 64-bit FNV-1a checksum of the payload.  Both calls block until the copy is done. */
+typedef struct rlcu_checkpoint_info {
+    uint64_t state_elems;     /* floats in each of m, v (and master)                   */
+    int32_t  step;            /* Adam step counter t                                   */
+    float    loss_scale;
+    int32_t  growth_tracker;
+    int32_t  skipped;
+    int32_t  rank, world;     /* which shard this is (0 of 1 without sharding)         */
+    uint32_t has_master;
+    uint32_t reserved;
+} rlcu_checkpoint_info;
+
+int rlcu_checkpoint_save(const char* path, const rlcu_checkpoint_info* info,
+                         const float* m, const float* v, const float* master, void* stream);
+/* header only; touches no device */
+int rlcu_checkpoint_peek(const char* path, rlcu_checkpoint_info* info_out);
+/* m / v / master must hold `capacity_elems` >= the file's state_elems floats; a
+ * file written with a master needs `master`, and the other way round. */
+int rlcu_checkpoint_load(const char* path, rlcu_checkpoint_info* info_out,
+                         float* m, float* v, float* master, uint64_t capacity_elems, void* stream);
+
 /* -------- host-side helpers --------------------------------------------- */
 /* 1 - powf(beta, t) in FP32 exactly as AdamWOptimizer::step (optimizer.h:121-122) */
 float rlcu_bias_correction(float beta, int step);

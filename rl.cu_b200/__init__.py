@@ -35,6 +35,7 @@ EXPORTS = [
     "rlcu_adamw_multi_step", "rlcu_bias_correction", "rlcu_gradstat_flat_noalloc",
     "rlcu_zero1_make_plan", "rlcu_zero1_plan_pieces", "rlcu_zero1_unique_id", "rlcu_zero1_create",
     "rlcu_zero1_step", "rlcu_zero1_poll_error", "rlcu_zero1_destroy",
+    "rlcu_checkpoint_save", "rlcu_checkpoint_peek", "rlcu_checkpoint_load",
 ]
 UNIQUE_ID_BYTES = 128
 PHASE_REDUCE_SCATTER, PHASE_STATISTICS, PHASE_UPDATE, PHASE_ALL_GATHER = 1, 2, 4, 8
@@ -92,7 +93,15 @@ class Zero1Plan(C.Structure):
                 ("lo", C.c_uint64), ("hi", C.c_uint64), ("pieces", C.c_uint64)]
 
 
+class CheckpointInfo(C.Structure):
+    """``rlcu_checkpoint_info``."""
+    _fields_ = [("state_elems", C.c_uint64), ("step", C.c_int32), ("loss_scale", C.c_float),
+                ("growth_tracker", C.c_int32), ("skipped", C.c_int32), ("rank", C.c_int32),
+                ("world", C.c_int32), ("has_master", C.c_uint32), ("reserved", C.c_uint32)]
+
+
 assert C.sizeof(TensorDesc) == 64 and C.sizeof(Stat) == 64 and C.sizeof(ScalerState) == 32
+assert C.sizeof(CheckpointInfo) == 40
 assert C.sizeof(Zero1Segment) == 16 and C.sizeof(Zero1Plan) == 48
 
 
@@ -142,6 +151,9 @@ def lib() -> C.CDLL:
     L.rlcu_zero1_step.argtypes = [vp, vp, f, f, vp, vp, u32, u32, vp]
     L.rlcu_zero1_poll_error.argtypes = [vp]
     L.rlcu_zero1_destroy.argtypes = [vp, C.c_int]
+    L.rlcu_checkpoint_save.argtypes = [C.c_char_p, vp, vp, vp, vp, vp]
+    L.rlcu_checkpoint_peek.argtypes = [C.c_char_p, vp]
+    L.rlcu_checkpoint_load.argtypes = [C.c_char_p, vp, vp, vp, vp, u64, vp]
     L.rlcu_bias_correction.argtypes = [f, C.c_int]
     L.rlcu_bias_correction.restype = f
     _lib = L
@@ -303,3 +315,24 @@ class Zero1:
             self.close()
         except Exception:
             pass
+
+
+# ---------------------------------------------------------------------------
+# optimizer-state checkpoint
+# ---------------------------------------------------------------------------
+
+def checkpoint_save(path, info: CheckpointInfo, m_ptr, v_ptr, master_ptr=None, stream=None):
+    check(lib().rlcu_checkpoint_save(os.fsencode(path), C.addressof(info), m_ptr, v_ptr, master_ptr, stream))
+
+
+def checkpoint_peek(path) -> CheckpointInfo:
+    info = CheckpointInfo()
+    check(lib().rlcu_checkpoint_peek(os.fsencode(path), C.addressof(info)))
+    return info
+
+
+def checkpoint_load(path, m_ptr, v_ptr, master_ptr, capacity_elems, stream=None) -> CheckpointInfo:
+    info = CheckpointInfo()
+    check(lib().rlcu_checkpoint_load(os.fsencode(path), C.addressof(info), m_ptr, v_ptr, master_ptr,
+                                     capacity_elems, stream))
+    return info

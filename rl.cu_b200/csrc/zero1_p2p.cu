@@ -38,23 +38,37 @@ __device__ __forceinline__ void square_accumulate(const F8& x, float unscale, fl
     }
 }
 
-// One group of 8 elements: sum over the ranks in rank order (FP32), one rounding to FP16.
-template <int WORLD>
-__device__ __forceinline__ void reduce_group(const PeerIn& peers, ptrdiff_t off, __half* dst,
-                                             float unscale, float (&acc)[4]) {
+// UB groups of 8 elements per thread: all loads (UB per rank) are issued before any
+// arithmetic; each group is summed over the ranks in rank order (FP32) and rounded
+// once to FP16.  Group u of the thread is `stride` groups after group u-1.
+template <int WORLD, int UB>
+__device__ __forceinline__ void reduce_groups(const PeerIn& peers, ptrdiff_t off, __half* dst,
+                                              ptrdiff_t stride, float unscale, float (&acc)[4]) {
+    constexpr int W = WORLD > 0 ? WORLD : kMaxWorld;
     const int n = WORLD > 0 ? WORLD : peers.n;
-    uint4 x[WORLD > 0 ? WORLD : kMaxWorld];
+    uint4 x[UB][W];
 #pragma unroll
-    for (int j = 0; j < (WORLD > 0 ? WORLD : kMaxWorld); j++)
-        if (j < n) x[j] = ld_h8(peers.base[j] + off);
-    F8 sum = h8_to_f8(x[0]);
+    for (int u = 0; u < UB; u++)
 #pragma unroll
-    for (int j = 1; j < (WORLD > 0 ? WORLD : kMaxWorld); j++)
-        if (j < n) add_h8(x[j], sum);
-    const uint4 r = f8_to_h8(sum);
-    *reinterpret_cast<uint4*>(dst) = r;        // default policy: the update pass reads it next
-    square_accumulate(h8_to_f8(r), unscale, acc);
+        for (int j = 0; j < W; j++)
+            if (j < n) x[u][j] = ld_h8(peers.base[j] + off + u * stride * kGroup);
+#pragma unroll
+    for (int u = 0; u < UB; u++) {
+        F8 sum = h8_to_f8(x[u][0]);
+#pragma unroll
+        for (int j = 1; j < W; j++)
+            if (j < n) add_h8(x[u][j], sum);
+        const uint4 r = f8_to_h8(sum);
+        *reinterpret_cast<uint4*>(dst + u * stride * kGroup) = r;   // default policy: the update pass reads it next
+        square_accumulate(h8_to_f8(r), unscale, acc);
+    }
 }
+
+// loads in flight per thread are capped at eight 16-byte vectors
+template <int WORLD>
+struct ReduceBatch {
+    static constexpr int value = WORLD == 1 ? 4 : WORLD == 2 ? 4 : WORLD == 4 ? 2 : 1;
+};
 
 template <int WORLD>
 __global__ void __launch_bounds__(kThreads)
@@ -82,8 +96,17 @@ reduce_stat_kernel(const WorkItem* __restrict__ table, uint32_t n_items,
         if (fl & RLCU_TENSOR_GRAD_ZERO) continue;
         const ptrdiff_t base_off = g - peers.local_base;
         const uint32_t groups = (fl & kItemVec16) ? count / kGroup : 0;
+        if (count == kChunk && (fl & kItemVec16)) {
+            constexpr int UB = ReduceBatch<WORLD>::value;
+#pragma unroll
+            for (int b = 0; b < kGroupsPerThread / UB; b++) {
+                const ptrdiff_t first = (ptrdiff_t)(threadIdx.x + b * UB * kThreads) * kGroup;
+                reduce_groups<WORLD, UB>(peers, base_off + first, g + first, kThreads, unscale, acc);
+            }
+            continue;
+        }
         for (uint32_t grp = threadIdx.x; grp < groups; grp += kThreads)
-            reduce_group<WORLD>(peers, base_off + (ptrdiff_t)grp * kGroup, g + (size_t)grp * kGroup, unscale, acc);
+            reduce_groups<WORLD, 1>(peers, base_off + (ptrdiff_t)grp * kGroup, g + (size_t)grp * kGroup, 0, unscale, acc);
         for (uint32_t i = groups * kGroup + threadIdx.x; i < count; i += kThreads) {
             float s = __half2float(peers.base[0][base_off + i]);
             for (int j = 1; j < n; j++) s = __fadd_rn(s, __half2float(peers.base[j][base_off + i]));
@@ -136,7 +159,7 @@ adamw_table_peer_kernel(const WorkItem* __restrict__ table, uint32_t n_items, St
 }
 
 struct Geometry {
-    int sms = 0, occ_reduce = 0, occ_update = 0;
+    int sms = 0, occ_reduce[5] = {0, 0, 0, 0, 0}, occ_update = 0;   // reduce: generic, 1, 2, 4, 8 ranks
 };
 
 int geometry(Geometry* out) {
@@ -150,9 +173,15 @@ int geometry(Geometry* out) {
     if (!have[dev]) {
         Geometry g;
         RLCU_CUDA(cudaDeviceGetAttribute(&g.sms, cudaDevAttrMultiProcessorCount, dev));
-        RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&g.occ_reduce, reduce_stat_kernel<0>, kThreads, 0));
+        RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&g.occ_reduce[0], reduce_stat_kernel<0>, kThreads, 0));
+        RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&g.occ_reduce[1], reduce_stat_kernel<1>, kThreads, 0));
+        RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&g.occ_reduce[2], reduce_stat_kernel<2>, kThreads, 0));
+        RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&g.occ_reduce[3], reduce_stat_kernel<4>, kThreads, 0));
+        RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&g.occ_reduce[4], reduce_stat_kernel<8>, kThreads, 0));
         RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&g.occ_update, adamw_table_peer_kernel, kThreads, 0));
-        if (g.occ_reduce < 1 || g.occ_update < 1) return set_error(RLCU_ERR_CUDA, "kernel does not fit on an SM");
+        for (int occ : g.occ_reduce)
+            if (occ < 1) return set_error(RLCU_ERR_CUDA, "kernel does not fit on an SM");
+        if (g.occ_update < 1) return set_error(RLCU_ERR_CUDA, "kernel does not fit on an SM");
         cache[dev] = g;
         have[dev] = true;
     }
@@ -170,7 +199,8 @@ int launch_reduce_stat(rlcu_tensor_list* list, const PeerIn& peers, float unscal
     const int rc = geometry(&g);
     if (rc) return rc;
     // the scratch of the list was sized for the statistics kernel's grid; stay within it
-    int grid = g.sms * g.occ_reduce;
+    const int variant = peers.n == 1 ? 1 : peers.n == 2 ? 2 : peers.n == 4 ? 3 : peers.n == 8 ? 4 : 0;
+    int grid = g.sms * g.occ_reduce[variant];
     if (grid > list->grid_stat) grid = list->grid_stat;
     if ((uint32_t)grid > list->n_items) grid = list->n_items ? (int)list->n_items : 1;
 #define RLCU_LAUNCH_REDUCE(W)                                                                   \
