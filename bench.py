@@ -198,7 +198,7 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = 1 << 26
+    sample = int(os.environ.get("RLCU_BENCH_SAMPLE", 1 << 26))     # parameters per timed step
     rate, sec, cores = cpu_port_step_rate(sample, args.steps, args.warmup, threads=0)
     line = {
         "impl": "reference", "metric": "adamw_params_per_sec", "value": rate, "unit": "params/s",

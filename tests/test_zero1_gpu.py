@@ -162,3 +162,57 @@ def test_sharded_step_on_several_gpus(pkg, O, tmp_path, world, mode):
         z = np.load(tmp_path / f"rank{r}.npz")
         outs.append({k: (z[k] if z[k].ndim else z[k].item()) for k in z.files})
     _check(pkg, O, world, outs, world == 2, mode)
+
+
+def _leaver(rank, world, port, out_dir):
+    """Rank 1 leaves after the first step, between steps, with nothing in flight.  The ranks agree
+    on the host (gloo) before every launch who is still there; when someone has left, nobody
+    launches, and the survivors abort the communicator instead of waiting on it."""
+    import sys
+    import torch
+    import torch.distributed as dist
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    sys.path.insert(0, os.path.join(root, "tests"))
+    import __graft_entry__ as entry
+    from oracle import oracle as O
+    pkg = entry.load_package()
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    box = [pkg.zero1_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    total, p, m, v, grads = _inputs(O, world)
+    plan = pkg.zero1_plan(SEGS, rank, world)
+    S, padded = int(plan.shard_elems), int(plan.padded_elems)
+    pool = lambda a: torch.from_numpy(np.concatenate([a, np.zeros(padded - total, np.uint16)]).view(np.int16)).cuda()
+    p_pool, g_pool = pool(p), pool(grads[rank])
+    m_sh, v_sh = torch.zeros(S, device="cuda"), torch.zeros(S, device="cuda")
+    stat = torch.zeros(16, device="cuda")
+    z = pkg.Zero1(box[0], rank, world, p_pool.data_ptr(), g_pool.data_ptr(), SEGS, m_sh.data_ptr(), v_sh.data_ptr(), None)
+    steps_done = 0
+    for t in (1, 2, 3):
+        staying = not (rank == 1 and t == 2)
+        votes = [None] * world
+        dist.all_gather_object(votes, staying)            # the host-side heartbeat
+        if not all(votes):
+            break
+        z.step(pkg.hparams(LR, B1, B2, EPS, t), stat.data_ptr(), 1.0, MAX_NORM, None, 0)
+        torch.cuda.synchronize()
+        z.poll_error()
+        steps_done += 1
+    after = p_pool.cpu().numpy().copy()
+    z.close(abort=True)                                    # no collective is pending on any rank
+    np.savez(os.path.join(out_dir, f"leave{rank}.npz"), steps=steps_done, p=after.view(np.uint16))
+    dist.destroy_process_group()
+
+
+def test_rank_leaving_between_steps_is_handled_on_the_host(pkg, O, tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    mp.spawn(_leaver, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    a, b = np.load(tmp_path / "leave0.npz"), np.load(tmp_path / "leave1.npz")
+    assert int(a["steps"]) == int(b["steps"]) == 1         # nobody launched the second step
+    assert np.array_equal(a["p"], b["p"])                  # and both hold the same parameters
