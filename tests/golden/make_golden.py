@@ -112,7 +112,7 @@ def main(out_path):
 
 
 if __name__ == "__main__":
-    default = os.path.join(ROOT, "gpurun_out", "adamw_ref_b200.npz")
+    default = os.path.join(ROOT, "tests", "golden", "adamw_ref_b200.npz")
     target = sys.argv[1] if len(sys.argv) > 1 else default
     os.makedirs(os.path.dirname(target), exist_ok=True)
     main(target)

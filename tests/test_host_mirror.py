@@ -1,7 +1,7 @@
 """The C++ AdamWOptimizer mirror (include/training/optimizer.h).
 
 CPU: it compiles against a stand-in for RL.cu's model header, and -- when a checkout of RL.cu
-sits at RLCU_REFERENCE (default /root/reference) -- RL.cu's own tests/test_adamw.cu compiles
+is found at the path in RLCU_REFERENCE (or the default below) -- RL.cu's own tests/test_adamw.cu compiles
 unchanged against it.  GPU: the mirror's test program runs and reports no failure."""
 import os
 import shutil

@@ -1,11 +1,11 @@
-"""Loss-scaled, ragged multi-tensor stress case (BASELINE config 5) on one GPU.
+"""Loss-scaled, ragged multi-tensor stress case (configuration 5 of the benchmark specification) on one GPU.
 
 Thousands of FP16 tensors with log-uniform sizes in [64, 4,194,304], gradients multiplied by
 a loss scale of 65536, non-finite values injected every fourth step.  The fused statistics
 pass must flag the overflow, the update must leave parameters and moments untouched on those
 steps and the device-side scaler must halve the scale; clean steps must match the oracle.
 The loss-scale semantics have no counterpart in RL.cu (parity unpinned): the oracle restates
-BASELINE's text."""
+that specification's text."""
 import os
 
 import numpy as np
@@ -104,7 +104,7 @@ def test_ragged_loss_scaled_steps_match_the_oracle(pkg, O):
 
 
 def test_ragged_full_size_properties(pkg):
-    """20,000 tensors with the sizes BASELINE specifies (the realised total is printed; it is
+    """20,000 tensors with the specified sizes (the realised total is printed; it is
     about 7.6e9 for the stated bounds, RLCU_RAGGED_HI lowers the upper bound).  Properties that do
     not depend on size: an overflowing step leaves checksums of p, m, v unchanged and halves the
     scale; a clean step changes every tensor; the statistics pass is deterministic; the

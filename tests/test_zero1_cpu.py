@@ -1,7 +1,7 @@
 """ZeRO-1 host logic without a GPU: the shard geometry computed by the library
 (rlcu_zero1_make_plan / rlcu_zero1_plan_pieces are pure host arithmetic) and the step
 protocol run by two gloo ranks on the CPU, with the oracle standing in for the kernels.
-The contract (BASELINE config 3): the sharded result equals the single-rank step on the
+The contract (configuration 3 of the benchmark specification): the sharded result equals the single-rank step on the
 averaged gradients."""
 import os
 import socket
