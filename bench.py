@@ -440,11 +440,25 @@ def run_sharded(args):
     v_sh = torch.zeros(S, dtype=torch.float32, device=dev)
     stat = torch.zeros(16, dtype=torch.float32, device=dev)
 
-    box = [pkg.zero1_unique_id() if rank == 0 else None]
-    dist.broadcast_object_list(box, src=0)
+    def create(mode):
+        box = [pkg.zero1_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        return pkg.Zero1(box[0], rank, world, p_pool.data_ptr(), g_pool.data_ptr(), segments,
+                         m_sh.data_ptr(), v_sh.data_ptr(), None, mode=mode)
+
     mode = pkg.ZERO1_P2P if args.zero1_mode == "p2p" else pkg.ZERO1_NCCL
-    z = pkg.Zero1(box[0], rank, world, p_pool.data_ptr(), g_pool.data_ptr(), segments,
-                  m_sh.data_ptr(), v_sh.data_ptr(), None, mode=mode)
+    mode_note = None
+    try:
+        z = create(mode)
+    except pkg.RlcuError as exc:
+        # Peer mapping needs pools that came from cudaMalloc (CUDA IPC); it fails on every rank
+        # alike, e.g. under an allocator that uses virtual-memory segments.  The NCCL exchange
+        # still runs the same kernels and is reported as what it is.
+        if mode != pkg.ZERO1_P2P:
+            raise
+        mode_note = f"peer-to-peer exchange unavailable ({exc}); ran the NCCL exchange"
+        mode = pkg.ZERO1_NCCL
+        z = create(mode)
     stream = torch.cuda.current_stream().cuda_stream
     lr, b1, b2, eps, max_norm = 1e-6, 0.9, 0.999, 1e-8, 1.0
     flags = pkg.STEP_ROUND_CLIP_FP16
@@ -560,7 +574,8 @@ def run_sharded(args):
                                    "ncclReduceScatter(sum, f16) + ncclAllReduce(1 double) + ncclAllGather(f16)",
                        "l2": "each rank streams its whole 1.2 GB gradient and parameter pools per step, far larger than L2",
                        "grad_restore": "device copy of the rank's gradient replica before each step, outside the timed intervals",
-                       "grad_norm": final.norm, "clip_active": int(final.clip_active)},
+                       "grad_norm": final.norm, "clip_active": int(final.clip_active),
+                       **({"note": mode_note} if mode_note else {})},
             "phases_ms": phase_ms,
             "link_gbs_per_direction": link_rates,
             "roofline": roof,
