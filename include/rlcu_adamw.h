@@ -63,9 +63,12 @@ enum {
     RLCU_STEP_DEVICE_BIAS_CORRECTION = 2u, /* take 1-beta^t from the statistics record
                                        (written by the statistics pass when a device-side
                                        scaler state is attached) instead of rlcu_hparams */
-    RLCU_STEP_ZERO_GRADS = 4u       /* write zeros over each gradient after reading it:
+    RLCU_STEP_ZERO_GRADS = 4u,      /* write zeros over each gradient after reading it:
                                        folds RL.cu's qwen3_gradients_zero (qwen3.cu:1109-1112)
                                        into the update                                   */
+    RLCU_STEP_BULK_COPY = 8u        /* move the update's HBM traffic with the bulk-copy engine
+                                       (cp.async.bulk through shared-memory stages) instead of
+                                       per-thread loads and stores; same results            */
 };
 
 /* flags of the statistics pass */
@@ -168,6 +171,14 @@ int rlcu_half_to_float(float* dst, const void* src, int64_t n, void* stream);
  * (optimizer.h:188-250).  Tensors with n == 0 are allowed and ignored. */
 int rlcu_tensor_list_create(const rlcu_tensor_desc* descs, uint64_t count, rlcu_tensor_list** out);
 int rlcu_tensor_list_destroy(rlcu_tensor_list* list);
+/* Synchronises with the device and reports whether a bounded wait inside a kernel
+ * launched on this list gave up since the last check (RLCU_ERR_TIMEOUT); only the
+ * RLCU_STEP_BULK_COPY update has such waits.  Clears the condition. */
+int rlcu_tensor_list_check(rlcu_tensor_list* list);
+/* Runs a one-thread kernel whose bounded wait is certain to run out (it waits on a
+ * barrier nothing completes) and reports it through the same path: the expected
+ * return value is RLCU_ERR_TIMEOUT, and the device stays usable afterwards. */
+int rlcu_selftest_bounded_wait(rlcu_tensor_list* list, void* stream);
 /* elements the update pass touches / elements the statistics pass reads */
 uint64_t rlcu_tensor_list_numel(const rlcu_tensor_list* list);
 uint64_t rlcu_tensor_list_stat_numel(const rlcu_tensor_list* list);

@@ -23,14 +23,14 @@ LIB_PATH = os.path.join(_HERE, "lib", "librlcu_b200.so")
 OK, ERR_INVALID, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_UNSUPPORTED = range(6)
 F16, F32 = 0, 1
 TENSOR_NORM_ONLY, TENSOR_GRAD_ZERO = 1, 2
-STEP_ROUND_CLIP_FP16, STEP_DEVICE_BIAS_CORRECTION, STEP_ZERO_GRADS = 1, 2, 4
+STEP_ROUND_CLIP_FP16, STEP_DEVICE_BIAS_CORRECTION, STEP_ZERO_GRADS, STEP_BULK_COPY = 1, 2, 4, 8
 STAT_PARTIAL = 1
 
 # every symbol include/rlcu_adamw.h declares
 EXPORTS = [
     "rlcu_abi_version", "rlcu_last_error", "rlcu_adamw_fp16_master", "rlcu_adamw_fp16",
     "rlcu_adamw_fp32", "rlcu_half_to_float", "rlcu_tensor_list_create",
-    "rlcu_tensor_list_destroy", "rlcu_tensor_list_numel", "rlcu_tensor_list_stat_numel",
+    "rlcu_tensor_list_destroy", "rlcu_tensor_list_check", "rlcu_selftest_bounded_wait", "rlcu_tensor_list_numel", "rlcu_tensor_list_stat_numel",
     "rlcu_tensor_list_work_items", "rlcu_gradstat", "rlcu_gradstat_finalize",
     "rlcu_adamw_multi_step", "rlcu_bias_correction", "rlcu_gradstat_flat_noalloc",
     "rlcu_zero1_make_plan", "rlcu_zero1_plan_pieces", "rlcu_zero1_unique_id", "rlcu_zero1_create",
@@ -137,6 +137,8 @@ def lib() -> C.CDLL:
     L.rlcu_half_to_float.argtypes = [vp, vp, i64, vp]
     L.rlcu_tensor_list_create.argtypes = [vp, u64, C.POINTER(vp)]
     L.rlcu_tensor_list_destroy.argtypes = [vp]
+    L.rlcu_tensor_list_check.argtypes = [vp]
+    L.rlcu_selftest_bounded_wait.argtypes = [vp, vp]
     for name in ("rlcu_tensor_list_numel", "rlcu_tensor_list_stat_numel", "rlcu_tensor_list_work_items"):
         getattr(L, name).argtypes = [vp]
         getattr(L, name).restype = u64
@@ -220,6 +222,10 @@ class TensorList:
 
     def step(self, hp: HParams, stat_ptr=None, step_flags=0, stream=None):
         check(lib().rlcu_adamw_multi_step(self.handle, C.addressof(hp), stat_ptr, step_flags, stream))
+
+    def check(self):
+        """Synchronise and raise if a bounded device-side wait gave up (bulk-copy update only)."""
+        check(lib().rlcu_tensor_list_check(self.handle))
 
     def close(self):
         if self.handle:

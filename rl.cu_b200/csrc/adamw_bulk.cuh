@@ -1,0 +1,162 @@
+// The update pass with its HBM traffic moved by the bulk-copy engine (TMA, 1-D
+// cp.async.bulk) through a ring of shared-memory stages instead of per-thread
+// loads and stores: one elected thread keeps several tiles of p/g/m/v in flight
+// per SM, the other threads only touch shared memory.
+//
+// Only full, 16-byte aligned FP16 work items take this route; everything else in
+// the table (ragged tails, FP32 tensors, statistics-only entries) is handled by
+// the direct code of adamw_update.cuh inside the same kernel.
+//
+// Waits on the load barriers are bounded: when a wait gives up the CTA records it
+// in the error word, drains its own copies (again bounded) and returns.
+#pragma once
+
+#include "adamw_update.cuh"
+
+namespace rlcu {
+
+constexpr int kBulkThreads = 512;
+constexpr int kBulkTile = 2048;                       // elements per stage
+constexpr int kBulkTilesPerItem = kChunk / kBulkTile;
+constexpr int kBulkStages = 6;
+constexpr int kBulkDepth = kBulkStages - 2;           // tiles loading ahead of the one in use
+constexpr int kBulkStageBytes = 32768;                // [m 8K][v 8K][master 8K][p 4K][g 4K]
+constexpr int kBulkSmemBytes = kBulkStages * kBulkStageBytes;
+constexpr uint32_t kBulkWaitTries = 1u << 18;
+static_assert(kChunk % kBulkTile == 0 && kBulkTile == kBulkThreads * 4, "tile geometry");
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
+}
+
+// Bounded wait for the phase with the given parity.  false = gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t tries = kBulkWaitTries) {
+    for (uint32_t i = 0; i < tries; i++) {
+        uint32_t done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+// global -> shared, completion counted in bytes on the stage's barrier
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// shared -> global, tracked by the issuing thread's bulk groups
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 :: "l"(dst), "r"(src_smem), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" :: "n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ bool bulk_eligible(const WorkItem& it) {
+    const uint32_t kind = it.flags & kItemKindMask;
+    return it.count == (uint32_t)kChunk && (it.flags & kItemVec16) && kind != kItemKindF32 &&
+           !(it.flags & RLCU_TENSOR_NORM_ONLY);
+}
+
+// Issues the loads of one tile into a stage (one thread).
+__device__ __forceinline__ void bulk_issue_tile(const WorkItem& it, int sub, unsigned char* stage, uint32_t bar) {
+    const size_t e = (size_t)sub * kBulkTile;
+    const bool master = (it.flags & kItemKindMask) == kItemKindF16Master;
+    const bool zero = (it.flags & RLCU_TENSOR_GRAD_ZERO) != 0;
+    const uint32_t bytes = 2u * kBulkTile * 4u + (master ? kBulkTile * 4u : kBulkTile * 2u) + (zero ? 0u : kBulkTile * 2u);
+    mbar_expect_tx(bar, bytes);
+    const uint32_t s = smem_u32(stage);
+    bulk_load(s, it.m + e, kBulkTile * 4, bar);
+    bulk_load(s + 8192, it.v + e, kBulkTile * 4, bar);
+    if (master) bulk_load(s + 16384, it.master + e, kBulkTile * 4, bar);
+    else bulk_load(s + 24576, static_cast<const __half*>(it.p) + e, kBulkTile * 2, bar);
+    if (!zero) bulk_load(s + 28672, static_cast<const __half*>(it.g) + e, kBulkTile * 2, bar);
+}
+
+// Issues the stores of one finished tile (one thread) and commits them as one group.
+__device__ __forceinline__ void bulk_store_tile(const WorkItem& it, int sub, unsigned char* stage, bool zero_grads) {
+    const size_t e = (size_t)sub * kBulkTile;
+    const bool master = (it.flags & kItemKindMask) == kItemKindF16Master;
+    const uint32_t s = smem_u32(stage);
+    bulk_store(it.m + e, s, kBulkTile * 4);
+    bulk_store(it.v + e, s + 8192, kBulkTile * 4);
+    if (master) bulk_store(it.master + e, s + 16384, kBulkTile * 4);
+    bulk_store(static_cast<__half*>(it.p) + e, s + 24576, kBulkTile * 2);
+    if (zero_grads && !(it.flags & RLCU_TENSOR_GRAD_ZERO))
+        bulk_store(const_cast<__half*>(static_cast<const __half*>(it.g)) + e, s + 28672, kBulkTile * 2);
+    bulk_commit();
+}
+
+// Four elements of the tile per thread, in place in shared memory.
+__device__ __forceinline__ void bulk_compute_tile(const WorkItem& it, unsigned char* stage, const StepConsts& c,
+                                                  const GradXform& xf) {
+    const bool master = (it.flags & kItemKindMask) == kItemKindF16Master;
+    const bool zero = (it.flags & RLCU_TENSOR_GRAD_ZERO) != 0;
+    const float decay = decay_factor(c.lr, it.wd);
+    const int t = threadIdx.x;
+    float4* sm = reinterpret_cast<float4*>(stage) + t;
+    float4* sv = reinterpret_cast<float4*>(stage + 8192) + t;
+    float4* sw = reinterpret_cast<float4*>(stage + 16384) + t;
+    uint2* sp = reinterpret_cast<uint2*>(stage + 24576) + t;
+    uint2* sg = reinterpret_cast<uint2*>(stage + 28672) + t;
+    float4 m = *sm, v = *sv;
+    float w[4], g[4];
+    if (master) {
+        const float4 x = *sw;
+        w[0] = x.x; w[1] = x.y; w[2] = x.z; w[3] = x.w;
+    } else {
+        const uint2 x = *sp;
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&x.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&x.y));
+        w[0] = a.x; w[1] = a.y; w[2] = b.x; w[3] = b.y;
+    }
+    if (zero) {
+        g[0] = g[1] = g[2] = g[3] = 0.0f;
+    } else {
+        const uint2 x = *sg;
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&x.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&x.y));
+        g[0] = a.x; g[1] = a.y; g[2] = b.x; g[3] = b.y;
+    }
+    float mm[4] = {m.x, m.y, m.z, m.w}, vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        float x = __fmul_rn(g[i], xf.coef);
+        if (xf.round_half) x = round_through_half(x);
+        w[i] = adamw_element(w[i], x, mm[i], vv[i], c, decay);
+    }
+    *sm = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    *sv = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    if (master) *sw = make_float4(w[0], w[1], w[2], w[3]);
+    __half2 lo = __floats2half2_rn(w[0], w[1]), hi = __floats2half2_rn(w[2], w[3]);
+    uint2 out;
+    out.x = *reinterpret_cast<uint32_t*>(&lo);
+    out.y = *reinterpret_cast<uint32_t*>(&hi);
+    *sp = out;
+    if (xf.zero_grads && !zero) *sg = make_uint2(0u, 0u);
+}
+
+}  // namespace rlcu

@@ -24,6 +24,7 @@
 #include <new>
 #include <vector>
 
+#include "adamw_bulk.cuh"
 #include "adamw_update.cuh"
 #include "host_util.h"
 #include "tensor_list.h"
@@ -70,6 +71,133 @@ adamw_table_kernel(const WorkItem* __restrict__ table, uint32_t n_items, StepCon
         process_item<false>(it, c, xf, PeerOut{});
         if (nidx >= n_items) break;
         idx = nidx;
+    }
+}
+
+// Multi-tensor update, bulk-copy variant: one CTA per SM; kBulkThreads consumer threads do
+// the arithmetic in shared memory while one thread of an extra warp drives cp.async.bulk
+// loads and stores through a ring of kBulkStages stages (see adamw_bulk.cuh).  Producer and
+// consumers meet only at the stages' full/empty barriers.
+__global__ void __launch_bounds__(kBulkThreads + 32, 1)
+adamw_table_bulk_kernel(const WorkItem* __restrict__ table, uint32_t n_items, StepConsts c,
+                        const rlcu_stat* __restrict__ stat, uint32_t step_flags,
+                        unsigned int* error_word) {
+    extern __shared__ __align__(128) unsigned char ring[];
+    __shared__ __align__(8) unsigned long long full_bar[kBulkStages];
+    __shared__ __align__(8) unsigned long long empty_bar[kBulkStages];
+    GradXform xf;
+    if (!resolve_step(stat, step_flags, c, xf)) {
+        if (!(step_flags & RLCU_STEP_ZERO_GRADS)) return;
+        for (uint32_t idx = blockIdx.x; idx < n_items; idx += gridDim.x) {
+            const WorkItem it = load_item(table, idx);
+            if (it.flags & (RLCU_TENSOR_NORM_ONLY | RLCU_TENSOR_GRAD_ZERO)) continue;
+            if ((it.flags & kItemKindMask) == kItemKindF32) {
+                float* g = const_cast<float*>(static_cast<const float*>(it.g));
+                for (uint32_t i = threadIdx.x; i < it.count; i += blockDim.x) g[i] = 0.0f;
+            } else {
+                __half* g = const_cast<__half*>(static_cast<const __half*>(it.g));
+                for (uint32_t i = threadIdx.x; i < it.count; i += blockDim.x) g[i] = __float2half_rn(0.0f);
+            }
+        }
+        return;
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kBulkStages; s++) {
+            mbar_init(smem_u32(&full_bar[s]), 1);                    // the producer's expect_tx
+            mbar_init(smem_u32(&empty_bar[s]), kBulkThreads / 32);   // one arrival per consumer warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (threadIdx.x >= kBulkThreads) {
+        // ---------------- producer warp: one thread issues every bulk copy ----------------
+        if (threadIdx.x != kBulkThreads) return;
+        uint32_t load_item_idx = blockIdx.x, loaded = 0;     // next tile to load
+        uint32_t store_item_idx = blockIdx.x, stored = 0;    // next tile to store
+        int load_sub = 0, store_sub = 0;
+        WorkItem lit, sit;
+        bool have_l = false, have_s = false, bail = false;
+        auto next_eligible = [&](uint32_t& idx, WorkItem& it, bool& have) {
+            while (!have && idx < n_items) {
+                it = load_item(table, idx);
+                if (bulk_eligible(it)) have = true;
+                else idx += gridDim.x;
+            }
+            return have;
+        };
+        auto load_upto = [&](uint32_t upto) {
+            while (loaded < upto && next_eligible(load_item_idx, lit, have_l)) {
+                const int stage = loaded % kBulkStages;
+                bulk_issue_tile(lit, load_sub, ring + (size_t)stage * kBulkStageBytes, smem_u32(&full_bar[stage]));
+                loaded++;
+                if (++load_sub == kBulkTilesPerItem) {
+                    load_sub = 0;
+                    load_item_idx += gridDim.x;
+                    have_l = false;
+                }
+            }
+        };
+        load_upto(kBulkDepth);
+        while (next_eligible(store_item_idx, sit, have_s)) {
+            const int stage = stored % kBulkStages;
+            // the consumers have finished tile `stored` in this stage
+            if (!mbar_wait(smem_u32(&empty_bar[stage]), (stored / kBulkStages) & 1u)) {
+                bail = true;
+                break;
+            }
+            bulk_store_tile(sit, store_sub, ring + (size_t)stage * kBulkStageBytes, xf.zero_grads);
+            stored++;
+            if (++store_sub == kBulkTilesPerItem) {
+                store_sub = 0;
+                store_item_idx += gridDim.x;
+                have_s = false;
+            }
+            bulk_wait_read<1>();                 // the stage refilled next was stored two tiles ago
+            load_upto(stored + kBulkDepth);
+        }
+        if (bail) {
+            atomicExch(error_word, 1u);
+            // loads already issued still land in this CTA's shared memory: wait for them (bounded)
+            for (uint32_t t = stored; t < loaded; t++)
+                mbar_wait(smem_u32(&full_bar[t % kBulkStages]), (t / kBulkStages) & 1u);
+        }
+        bulk_wait_all();
+        return;
+    }
+
+    // ---------------- consumer warps ----------------
+    uint32_t tiles = 0;
+    for (uint32_t idx = blockIdx.x; idx < n_items; idx += gridDim.x) {
+        const WorkItem it = load_item(table, idx);
+        if (!bulk_eligible(it)) {
+            if (threadIdx.x < kThreads) process_item<false>(it, c, xf, PeerOut{});
+            continue;
+        }
+        for (int sub = 0; sub < kBulkTilesPerItem; sub++) {
+            const int stage = tiles % kBulkStages;
+            if (!mbar_wait(smem_u32(&full_bar[stage]), (tiles / kBulkStages) & 1u)) {
+                atomicExch(error_word, 1u);      // stop arriving: the producer's wait runs out too
+                return;
+            }
+            bulk_compute_tile(it, ring + (size_t)stage * kBulkStageBytes, c, xf);
+            fence_async_smem();                  // results visible to the bulk store
+            __syncwarp();
+            if ((threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
+            tiles++;
+        }
+    }
+}
+
+// Exercises the give-up path of the bounded barrier wait: waits on a barrier that
+// nothing will ever complete, with a small try budget, and records the outcome the way
+// the bulk-copy update does.  The kernel returns normally; the context stays usable.
+__global__ void bounded_wait_probe_kernel(unsigned int* error_word, uint32_t tries) {
+    __shared__ __align__(8) unsigned long long bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (!mbar_wait(smem_u32(&bar), 0u, tries)) atomicExch(error_word, 1u);
     }
 }
 
@@ -556,6 +684,24 @@ int rlcu_tensor_list_destroy(rlcu_tensor_list* list) {
     return RLCU_OK;
 }
 
+int rlcu_tensor_list_check(rlcu_tensor_list* list) {
+    if (!list) return set_error(RLCU_ERR_INVALID, "null list");
+    unsigned int word = 0;
+    RLCU_CUDA(cudaMemcpy(&word, list->d_counter + 16, sizeof(word), cudaMemcpyDeviceToHost));
+    if (word) {
+        cudaMemset(list->d_counter + 16, 0, sizeof(word));
+        return set_error(RLCU_ERR_TIMEOUT, "a bulk-copy wait in the update kernel gave up; the step is incomplete");
+    }
+    return RLCU_OK;
+}
+
+int rlcu_selftest_bounded_wait(rlcu_tensor_list* list, void* stream) {
+    if (!list) return set_error(RLCU_ERR_INVALID, "null list");
+    bounded_wait_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(list->d_counter + 16, 64u);
+    RLCU_CUDA(cudaGetLastError());
+    return rlcu_tensor_list_check(list);
+}
+
 uint64_t rlcu_tensor_list_numel(const rlcu_tensor_list* list) { return list ? list->numel : 0; }
 uint64_t rlcu_tensor_list_stat_numel(const rlcu_tensor_list* list) { return list ? list->stat_numel : 0; }
 uint64_t rlcu_tensor_list_work_items(const rlcu_tensor_list* list) { return list ? list->n_items : 0; }
@@ -583,11 +729,32 @@ int rlcu_gradstat_finalize(rlcu_stat* stat, float unscale, float max_norm,
 int rlcu_adamw_multi_step(rlcu_tensor_list* list, const rlcu_hparams* hp,
                           const rlcu_stat* stat, uint32_t step_flags, void* stream) {
     if (!list || !hp) return set_error(RLCU_ERR_INVALID, "null list or hparams");
-    const uint32_t known = RLCU_STEP_ROUND_CLIP_FP16 | RLCU_STEP_DEVICE_BIAS_CORRECTION | RLCU_STEP_ZERO_GRADS;
+    const uint32_t known = RLCU_STEP_ROUND_CLIP_FP16 | RLCU_STEP_DEVICE_BIAS_CORRECTION | RLCU_STEP_ZERO_GRADS |
+                           RLCU_STEP_BULK_COPY;
     if (step_flags & ~known) return set_error(RLCU_ERR_INVALID, "unknown step flags");
     if ((step_flags & RLCU_STEP_DEVICE_BIAS_CORRECTION) && !stat)
         return set_error(RLCU_ERR_INVALID, "device bias correction needs a statistics record");
     if (list->n_items == 0) return RLCU_OK;
+    if (step_flags & RLCU_STEP_BULK_COPY) {
+        DeviceInfo di;
+        const int rc = device_info(&di);
+        if (rc) return rc;
+        static bool configured[64] = {};
+        int dev = 0;
+        RLCU_CUDA(cudaGetDevice(&dev));
+        if (!configured[dev]) {
+            RLCU_CUDA(cudaFuncSetAttribute(adamw_table_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kBulkSmemBytes));
+            configured[dev] = true;
+        }
+        const int grid = (int)(list->n_items < (uint32_t)di.sms ? list->n_items : (uint32_t)di.sms);
+        adamw_table_bulk_kernel<<<grid, kBulkThreads + 32, kBulkSmemBytes, (cudaStream_t)stream>>>(
+            list->d_items, list->n_items,
+            make_consts(hp->lr, hp->beta1, hp->beta2, hp->eps, hp->bias_correction1, hp->bias_correction2),
+            stat, step_flags & ~(uint32_t)RLCU_STEP_BULK_COPY, list->d_counter + 16);
+        RLCU_CUDA(cudaGetLastError());
+        return RLCU_OK;
+    }
     adamw_table_kernel<<<list->grid_update, kThreads, 0, (cudaStream_t)stream>>>(
         list->d_items, list->n_items,
         make_consts(hp->lr, hp->beta1, hp->beta2, hp->eps, hp->bias_correction1, hp->bias_correction2),

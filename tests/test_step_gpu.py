@@ -476,3 +476,40 @@ def test_config2_full_size_vs_reference_kernels(pkg, O, torch):
         a, b = mine[name], ref[name]
         view = torch.int16 if a.dtype == torch.float16 else torch.int32
         assert torch.equal(a.view(view), b.view(view)), f"{name}: differs from the reference kernels"
+
+
+@pytest.mark.parametrize("extra", [0, "zero_grads"])
+def test_bulk_copy_update_equals_the_direct_update(pkg, O, torch, extra):
+    """The cp.async.bulk (TMA) variant of the update kernel against the per-thread load/store
+    one, bit for bit, on a list that mixes full work items with ragged, unaligned, FP32 and
+    statistics-only entries."""
+    specs = [(8192 * 5, "h", 0.01, 0), (100, "h", 0.0, 0), (8192 * 3 + 17, "hm", 0.01, 0), (8192, "hm", 0.0, 0),
+             (8192 * 9, "h", 0.01, 0), (5, "f", 0.0, 0), (8192 * 2, "f", 0.01, 0), (8192 * 4, "hm", 0.0, pkg.TENSOR_GRAD_ZERO),
+             (3000, "f", 0.0, pkg.TENSOR_NORM_ONLY)]
+    flags = pkg.STEP_ROUND_CLIP_FP16 | (pkg.STEP_ZERO_GRADS if extra else 0)
+    results = []
+    for bulk in (0, pkg.STEP_BULK_COPY):
+        host, dev, descs = make_case(O, torch, pkg, specs, seed=81)
+        tl = pkg.TensorList(descs)
+        stat = torch.zeros(16, device="cuda")
+        tl.gradstat(stat.data_ptr(), 1.0, 1.0)
+        for t in (2, 3, 4):
+            tl.step(pkg.hparams(1e-4, 0.9, 0.999, 1e-8, t), stat.data_ptr(), flags | bulk)
+        tl.check()
+        results.append([{k: b.get() for k, b in d.items()} for d in dev])
+        assert all(b.guards_intact() for d in dev for b in d.values())
+    for a, b in zip(*results):
+        for k in a:
+            assert np.array_equal(a[k].view(np.uint8), b[k].view(np.uint8)), k
+
+
+def test_bounded_wait_gives_up_and_reports(pkg, torch):
+    """A device-side wait that nothing satisfies runs out of tries, the kernel returns, the host
+    reads RLCU_ERR_TIMEOUT, and the GPU keeps working."""
+    a = torch.zeros(64, device="cuda")
+    tl = pkg.TensorList([pkg.TensorDesc(a.data_ptr(), a.data_ptr(), a.data_ptr(), a.data_ptr(), None, 8, 0.0, pkg.F32, 0, 0)])
+    rc = pkg.lib().rlcu_selftest_bounded_wait(tl.handle, None)
+    assert rc == pkg.ERR_TIMEOUT and b"gave up" in pkg.lib().rlcu_last_error()
+    tl.check()                                           # the condition was cleared
+    tl.step(pkg.hparams(1e-3, 0.9, 0.999, 1e-8, 1))      # and the device still runs kernels
+    torch.cuda.synchronize()
