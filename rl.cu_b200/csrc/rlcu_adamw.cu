@@ -443,6 +443,9 @@ int device_info(DeviceInfo* out) {
         RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&di.occ_table, adamw_table_kernel, kThreads, 0));
         RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&di.occ_flat, adamw_flat_kernel, kThreads, 0));
         RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&di.occ_stat, gradstat_kernel, kThreads, 0));
+        // the bulk-copy variant needs its 192 KB ring opted in once per device
+        RLCU_CUDA(cudaFuncSetAttribute(adamw_table_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kBulkSmemBytes));
         if (di.occ_table < 1 || di.occ_flat < 1 || di.occ_stat < 1)
             return set_error(RLCU_ERR_CUDA, "kernel does not fit on an SM");
         cache[dev] = di;
@@ -739,14 +742,6 @@ int rlcu_adamw_multi_step(rlcu_tensor_list* list, const rlcu_hparams* hp,
         DeviceInfo di;
         const int rc = device_info(&di);
         if (rc) return rc;
-        static bool configured[64] = {};
-        int dev = 0;
-        RLCU_CUDA(cudaGetDevice(&dev));
-        if (!configured[dev]) {
-            RLCU_CUDA(cudaFuncSetAttribute(adamw_table_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           kBulkSmemBytes));
-            configured[dev] = true;
-        }
         const int grid = (int)(list->n_items < (uint32_t)di.sms ? list->n_items : (uint32_t)di.sms);
         adamw_table_bulk_kernel<<<grid, kBulkThreads + 32, kBulkSmemBytes, (cudaStream_t)stream>>>(
             list->d_items, list->n_items,

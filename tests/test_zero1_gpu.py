@@ -216,3 +216,65 @@ def test_rank_leaving_between_steps_is_handled_on_the_host(pkg, O, tmp_path):
     a, b = np.load(tmp_path / "leave0.npz"), np.load(tmp_path / "leave1.npz")
     assert int(a["steps"]) == int(b["steps"]) == 1         # nobody launched the second step
     assert np.array_equal(a["p"], b["p"])                  # and both hold the same parameters
+
+
+@pytest.mark.parametrize("mode", [0, 1], ids=["nccl", "p2p"])
+def test_sharded_step_with_device_scaler_skips_on_overflow(pkg, O, mode):
+    """Loss scaling through the sharded step (world 1 here): the scaler's grad_mul carries
+    1/world, a non-finite gradient makes every rank skip and halve the scale, a clean step
+    matches the oracle."""
+    import torch
+    torch.cuda.set_device(0)
+    total, p, m, v, grads = _inputs(O, 1)
+    plan = pkg.zero1_plan(SEGS, 0, 1)
+    S, padded = int(plan.shard_elems), int(plan.padded_elems)
+    scale = 1024.0
+
+    def pool(a):
+        out = np.zeros(padded, np.uint16)
+        out[:total] = a
+        return torch.from_numpy(out.view(np.int16)).cuda()
+
+    g_scaled = O.f2h(O.h2f(grads[0]) * np.float32(scale))
+    p_pool, g_pool = pool(p), pool(g_scaled)
+    m_sh = torch.from_numpy(np.concatenate([m, np.zeros(padded - total, np.float32)])).cuda()
+    v_sh = torch.from_numpy(np.concatenate([v, np.zeros(padded - total, np.float32)])).cuda()
+    dt = np.dtype([("scale", "f4"), ("gt", "i4"), ("step", "i4"), ("skipped", "i4"),
+                   ("interval", "i4"), ("b1", "f4"), ("b2", "f4"), ("mul", "f4")])
+    sc = np.zeros(1, dt)
+    sc["scale"], sc["interval"], sc["b1"], sc["b2"], sc["mul"], sc["step"] = scale, 1000, B1, B2, 1.0, T - 1
+    scaler = torch.from_numpy(sc.view(np.uint8).copy()).cuda()
+    stat = torch.zeros(16, device="cuda")
+    z = pkg.Zero1(pkg.zero1_unique_id(), 0, 1, p_pool.data_ptr(), g_pool.data_ptr(), SEGS,
+                  m_sh.data_ptr(), v_sh.data_ptr(), None, mode=mode)
+    hp = pkg.HParams(LR, B1, B2, EPS, 1.0, 1.0)
+    # overflowing step first
+    bad = g_scaled.copy()
+    bad[12345] = 0x7C00
+    g_pool.copy_(pool(bad))
+    before = (p_pool.clone(), m_sh.clone(), v_sh.clone())
+    z.step(hp, stat.data_ptr(), 1.0, MAX_NORM, scaler.data_ptr(), pkg.STEP_DEVICE_BIAS_CORRECTION)
+    torch.cuda.synchronize()
+    s = read_stat(pkg, stat)
+    got = np.frombuffer(scaler.cpu().numpy().tobytes(), dtype=dt)[0]
+    assert s.found_inf == 1 and got["scale"] == scale / 2 and got["step"] == T - 1 and got["skipped"] == 1
+    assert torch.equal(before[0], p_pool) and torch.equal(before[1], m_sh) and torch.equal(before[2], v_sh)
+    # clean step with gradients carrying the halved scale
+    g_half = O.f2h(O.h2f(grads[0]) * np.float32(scale / 2))
+    g_pool.copy_(pool(g_half))
+    z.step(hp, stat.data_ptr(), 1.0, MAX_NORM, scaler.data_ptr(), pkg.STEP_DEVICE_BIAS_CORRECTION)
+    torch.cuda.synchronize()
+    s = read_stat(pkg, stat)
+    assert s.found_inf == 0 and s.step == T and s.loss_scale == scale / 2
+    entries, off = [], 0
+    for n, wd, fl in SEGS:
+        entries.append(dict(p=p[off:off + n], g=g_half[off:off + n], m=m[off:off + n], v=v[off:off + n], wd=wd, flags=fl))
+        off += n
+    ts = O.make_tensors(entries)
+    want = O.gradstat(ts, 2.0 / scale, MAX_NORM)
+    assert abs(s.norm - want.norm) <= 1e-5 * want.norm
+    O.multi_step(ts, O.HParams(LR, B1, B2, EPS, s.bias_correction1, s.bias_correction2),
+                 O.gradstat_finalize(s.sum_sq, 0, 2.0 / scale, MAX_NORM), 0)
+    assert np.array_equal(p_pool.cpu().numpy().view(np.uint16)[:total], p)
+    assert np.array_equal(m_sh.cpu().numpy()[:total], m) and np.array_equal(v_sh.cpu().numpy()[:total], v)
+    z.close()
