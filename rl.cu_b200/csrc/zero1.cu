@@ -197,9 +197,12 @@ int setup_p2p(rlcu_zero1* z) {
     std::vector<PoolExport> all(W);
     PoolExport* d_all = nullptr;
     RLCU_CUDA(cudaMalloc(&d_all, sizeof(PoolExport) * W));
-    RLCU_CUDA(cudaMemcpy(d_all + z->rank, &mine, sizeof(PoolExport), cudaMemcpyHostToDevice));
-    ncclResult_t nr = z->api->AllGather(d_all + z->rank, d_all, sizeof(PoolExport), ncclInt8, z->comm, 0);
-    cudaError_t ce = cudaStreamSynchronize(0);
+    cudaError_t ce = cudaMemcpy(d_all + z->rank, &mine, sizeof(PoolExport), cudaMemcpyHostToDevice);
+    ncclResult_t nr = ncclSuccess;
+    if (ce == cudaSuccess) {
+        nr = z->api->AllGather(d_all + z->rank, d_all, sizeof(PoolExport), ncclInt8, z->comm, 0);
+        ce = cudaStreamSynchronize(0);
+    }
     if (nr == ncclSuccess && ce == cudaSuccess)
         ce = cudaMemcpy(all.data(), d_all, sizeof(PoolExport) * W, cudaMemcpyDeviceToHost);
     cudaFree(d_all);
