@@ -278,3 +278,107 @@ def test_sharded_step_with_device_scaler_skips_on_overflow(pkg, O, mode):
     assert np.array_equal(p_pool.cpu().numpy().view(np.uint16)[:total], p)
     assert np.array_equal(m_sh.cpu().numpy()[:total], m) and np.array_equal(v_sh.cpu().numpy()[:total], v)
     z.close()
+
+
+def _overflow_worker(rank, world, port, out_dir, mode):
+    import sys
+    import torch
+    import torch.distributed as dist
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    sys.path.insert(0, os.path.join(root, "tests"))
+    import __graft_entry__ as entry
+    from oracle import oracle as O
+    pkg = entry.load_package()
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    box = [pkg.zero1_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    total, p, m, v, grads = _inputs(O, world)
+    plan = pkg.zero1_plan(SEGS, rank, world)
+    S, padded = int(plan.shard_elems), int(plan.padded_elems)
+    lo = rank * S
+    scale = 256.0
+
+    def pool(a):
+        out = np.zeros(padded, np.uint16)
+        out[:total] = a
+        return torch.from_numpy(out.view(np.int16)).cuda()
+
+    def shard(a):
+        out = np.zeros(padded, np.float32)
+        out[:total] = a
+        return torch.from_numpy(out[lo:lo + S].copy()).cuda()
+
+    mine = O.f2h(O.h2f(grads[rank]) * np.float32(scale))
+    bad = mine.copy()
+    if rank == 1:
+        bad[7] = 0xFC00                     # -inf in ONE rank's replica, in the OTHER rank's shard
+    p_pool, g_pool = pool(p), pool(bad)
+    m_sh, v_sh = shard(m), shard(v)
+    dt = np.dtype([("scale", "f4"), ("gt", "i4"), ("step", "i4"), ("skipped", "i4"),
+                   ("interval", "i4"), ("b1", "f4"), ("b2", "f4"), ("mul", "f4")])
+    sc = np.zeros(1, dt)
+    sc["scale"], sc["interval"], sc["b1"], sc["b2"], sc["mul"], sc["step"] = scale, 1000, B1, B2, 1.0 / world, T - 1
+    scaler = torch.from_numpy(sc.view(np.uint8).copy()).cuda()
+    stat = torch.zeros(16, device="cuda")
+    z = pkg.Zero1(box[0], rank, world, p_pool.data_ptr(), g_pool.data_ptr(), SEGS, m_sh.data_ptr(), v_sh.data_ptr(),
+                  None, mode=mode)
+    hp = pkg.HParams(LR, B1, B2, EPS, 1.0, 1.0)
+    z.step(hp, stat.data_ptr(), 1.0, MAX_NORM, scaler.data_ptr(), pkg.STEP_DEVICE_BIAS_CORRECTION)
+    torch.cuda.synchronize()
+    s1 = stat.cpu().numpy().copy()
+    sc1 = scaler.cpu().numpy().copy()
+    untouched = bool(np.array_equal(p_pool.cpu().numpy().view(np.uint16)[:total], p))
+    g_pool.copy_(pool(O.f2h(O.h2f(grads[rank]) * np.float32(scale / 2))))
+    z.step(hp, stat.data_ptr(), 1.0, MAX_NORM, scaler.data_ptr(), pkg.STEP_DEVICE_BIAS_CORRECTION)
+    torch.cuda.synchronize()
+    np.savez(os.path.join(out_dir, f"ovf{rank}.npz"), s1=s1, sc1=sc1, untouched=untouched, s2=stat.cpu().numpy(),
+             sc2=scaler.cpu().numpy(), p=p_pool.cpu().numpy().view(np.uint16), g=g_pool.cpu().numpy().view(np.uint16),
+             m=m_sh.cpu().numpy(), v=v_sh.cpu().numpy(), lo=lo, S=S)
+    z.close()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", [0, 1], ids=["nccl", "p2p"])
+def test_overflow_in_one_replica_skips_every_rank(pkg, O, tmp_path, mode):
+    """A non-finite gradient in one rank's replica reaches every rank through the reduced sum of
+    squares: all ranks skip, all halve the scale; the next clean step equals the oracle."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    mp.spawn(_overflow_worker, args=(world, _free_port(), str(tmp_path), mode), nprocs=world, join=True)
+    dt = np.dtype([("scale", "f4"), ("gt", "i4"), ("step", "i4"), ("skipped", "i4"),
+                   ("interval", "i4"), ("b1", "f4"), ("b2", "f4"), ("mul", "f4")])
+    outs = [np.load(tmp_path / f"ovf{r}.npz") for r in range(world)]
+    total, p, m, v, grads = _inputs(O, world)
+    scale = 256.0
+    for o in outs:
+        s1 = pkg.Stat.from_buffer_copy(o["s1"].tobytes())
+        sc1 = np.frombuffer(o["sc1"].tobytes(), dtype=dt)[0]
+        assert s1.found_inf == 1 and bool(o["untouched"])
+        assert sc1["scale"] == scale / 2 and sc1["skipped"] == 1 and sc1["step"] == T - 1
+        s2 = pkg.Stat.from_buffer_copy(o["s2"].tobytes())
+        assert s2.found_inf == 0 and s2.step == T and s2.loss_scale == scale / 2
+    S = int(outs[0]["S"])
+    g_sum = np.zeros(total, np.uint16)
+    for o in outs:
+        lo, hi = int(o["lo"]), min(int(o["lo"]) + S, total)
+        g_sum[lo:hi] = o["g"][lo:hi]
+    s2 = pkg.Stat.from_buffer_copy(outs[0]["s2"].tobytes())
+    entries, off = [], 0
+    for n, wd, fl in SEGS:
+        entries.append(dict(p=p[off:off + n], g=g_sum[off:off + n], m=m[off:off + n], v=v[off:off + n], wd=wd, flags=fl))
+        off += n
+    ts = O.make_tensors(entries)
+    unscale = (1.0 / world) / (scale / 2)
+    O.multi_step(ts, O.HParams(LR, B1, B2, EPS, s2.bias_correction1, s2.bias_correction2),
+                 O.gradstat_finalize(s2.sum_sq, 0, unscale, MAX_NORM), 0)
+    for o in outs:
+        assert np.array_equal(o["p"][:total], p)
+        lo, hi = int(o["lo"]), min(int(o["lo"]) + S, total)
+        assert np.array_equal(o["m"][:hi - lo], m[lo:hi]) and np.array_equal(o["v"][:hi - lo], v[lo:hi])
