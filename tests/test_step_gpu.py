@@ -513,3 +513,45 @@ def test_bounded_wait_gives_up_and_reports(pkg, torch):
     tl.check()                                           # the condition was cleared
     tl.step(pkg.hparams(1e-3, 0.9, 0.999, 1e-8, 1))      # and the device still runs kernels
     torch.cuda.synchronize()
+
+
+def test_step_replays_from_a_cuda_graph(pkg, O, torch):
+    """The whole step (statistics + update, step counter and bias corrections kept on the
+    device) has no host round trip, so it can be captured once and replayed: five replays give
+    the bits of five eager steps."""
+    specs = [(8192 * 6 + 40, "h", 0.01, 0), (5000, "hm", 0.0, 0), (700, "f", 0.0, 0)]
+    dt = np.dtype([("scale", "f4"), ("gt", "i4"), ("step", "i4"), ("skipped", "i4"),
+                   ("interval", "i4"), ("b1", "f4"), ("b2", "f4"), ("mul", "f4")])
+
+    def scaler():
+        sc = np.zeros(1, dt)
+        sc["scale"], sc["interval"], sc["b1"], sc["b2"] = 1.0, 1 << 30, 0.9, 0.999
+        return torch.from_numpy(sc.view(np.uint8).copy()).cuda()
+
+    hp = pkg.HParams(1e-4, 0.9, 0.999, 1e-8, 1.0, 1.0)
+    flags = pkg.STEP_DEVICE_BIAS_CORRECTION | pkg.STEP_ROUND_CLIP_FP16
+    _, dev_a, descs_a = make_case(O, torch, pkg, specs, seed=91)
+    _, dev_b, descs_b = make_case(O, torch, pkg, specs, seed=91)
+    ta, tb = pkg.TensorList(descs_a), pkg.TensorList(descs_b)
+    sa, sb, stat_a, stat_b = scaler(), scaler(), torch.zeros(16, device="cuda"), torch.zeros(16, device="cuda")
+    for _ in range(5):                                   # eager
+        ta.gradstat(stat_a.data_ptr(), 1.0, 0.5, scaler_ptr=sa.data_ptr())
+        ta.step(hp, stat_a.data_ptr(), flags)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        tb.gradstat(stat_b.data_ptr(), 1.0, 0.5, scaler_ptr=sb.data_ptr(), stream=side.cuda_stream)   # set-up outside capture
+        tb.step(hp, stat_b.data_ptr(), flags, stream=side.cuda_stream)
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            s = torch.cuda.current_stream().cuda_stream
+            tb.gradstat(stat_b.data_ptr(), 1.0, 0.5, scaler_ptr=sb.data_ptr(), stream=s)
+            tb.step(hp, stat_b.data_ptr(), flags, stream=s)
+    for _ in range(4):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert read_stat(pkg, stat_a).step == read_stat(pkg, stat_b).step == 5
+    for da, db in zip(dev_a, dev_b):
+        for k in da:
+            assert np.array_equal(da[k].get().view(np.uint8), db[k].get().view(np.uint8)), k
