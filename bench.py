@@ -244,7 +244,7 @@ def run_single(args):
     tl = pkg.TensorList(make_descs(pkg, pools, shapes, wd, align=args.align))
     stat = torch.zeros(16, dtype=torch.float32, device=dev)
     stream = torch.cuda.current_stream().cuda_stream
-    flags = pkg.STEP_ROUND_CLIP_FP16
+    flags = pkg.STEP_ROUND_CLIP_FP16 | (pkg.STEP_BULK_COPY if args.bulk else 0)
 
     def step(t):
         tl.gradstat(stat.data_ptr(), 1.0, max_norm, stream=stream)
@@ -604,6 +604,8 @@ def main():
                     help="N>1: fused peer-to-peer kernels (default) or NCCL reduce-scatter/all-gather")
     ap.add_argument("--align", type=int, default=8,
                     help="N=1: elements every tensor start is aligned to inside the pools (8 = 16 bytes)")
+    ap.add_argument("--bulk", action="store_true",
+                    help="N=1: run the update through the cp.async.bulk variant of the kernel")
     ap.add_argument("--quick", action="store_true",
                     help="device-resident timing only (no end-to-end, CPU or reference-kernel legs): for profiler runs")
     args = ap.parse_args()
