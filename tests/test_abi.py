@@ -26,8 +26,15 @@ def test_exports_every_declared_symbol(pkg):
     assert declared, "no declarations found"
     for name in sorted(declared):
         assert hasattr(L, name), f"{name} is declared in include/ but not exported"
-    assert declared == set(pkg.EXPORTS) | {n for n in declared if n.startswith("rlcu_zero1")} or \
-        declared >= set(pkg.EXPORTS)
+    assert declared == set(pkg.EXPORTS), "the binding's export list and the header disagree"
+
+
+def test_missing_library_fails_loudly(pkg, monkeypatch):
+    """No fallback implementation: without the shared library the binding refuses to work."""
+    monkeypatch.setattr(pkg, "_lib", None)
+    monkeypatch.setattr(pkg, "LIB_PATH", "/nonexistent/librlcu_b200.so")
+    with pytest.raises(ImportError):
+        pkg.lib()
 
 
 def test_exports_reference_launchers(pkg):
