@@ -50,3 +50,37 @@ def test_mirror_program_passes_on_the_gpu(mirror_binary):
     print(r.stdout)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "[FAIL]" not in r.stdout and r.stdout.count("[PASS]") >= 13
+
+
+def test_reference_test_binary_links_against_the_library(pkg, tmp_path):
+    """Link-level drop-in: RL.cu's tests/test_adamw.cu with RL.cu's own headers and every RL.cu
+    source except src/kernels/adamw.cu links into an executable whose launch_adamw_fp16 /
+    launch_adamw_fp32 come from librlcu_b200.so.  (Running it needs real Qwen3-0.6B weights, which
+    are not here; it exits at once without them, tests/test_adamw.cu:507-510.)"""
+    import glob
+    import sysconfig
+    src = os.path.join(REF, "tests", "test_adamw.cu")
+    if not os.path.exists(src) or shutil.which("nvcc") is None:
+        pytest.skip("no checkout of RL.cu here")
+    site = sysconfig.get_paths()["purelib"]
+    json_hpp = glob.glob(os.path.join(site, "include", "cudnn_frontend", "thirdparty", "nlohmann", "json.hpp"))
+    xxhash_h = glob.glob(os.path.join(site, "pyarrow", "include", "arrow", "vendored", "xxhash", "xxhash.h"))
+    if not json_hpp or not xxhash_h:
+        pytest.skip("nlohmann/json or xxhash, which RL.cu expects under third_party/, is not installed")
+    shim = tmp_path / "shim" / "third_party"
+    shim.mkdir(parents=True)
+    os.symlink(json_hpp[0], shim / "json.hpp")
+    os.symlink(xxhash_h[0], shim / "xxhash.h")
+    sources = [s for pat in ("src/kernels/*.cu", "src/kernels/*.cpp", "src/model/*.cu")
+               for s in sorted(glob.glob(os.path.join(REF, pat))) if not s.endswith("kernels/adamw.cu")]
+    lib_dir = os.path.join(ROOT, "rl.cu_b200", "lib")
+    exe = str(tmp_path / "test_adamw")
+    cmd = ["nvcc", "-std=c++17", "-O0", "--expt-relaxed-constexpr", "-w", "-gencode", "arch=compute_100a,code=sm_100a",
+           "-I", os.path.join(REF, "include"), "-I", str(tmp_path / "shim"), src] + sources + \
+          ["-o", exe, "-lcublas", "-L", lib_dir, "-lrlcu_b200", "-Xlinker", f"-rpath={lib_dir}"]
+    subprocess.run(cmd, check=True)
+    undefined = subprocess.run(["nm", "-D", "--undefined-only", exe], check=True, capture_output=True, text=True).stdout
+    for sym in pkg.CXX_EXPORTS:
+        assert sym in undefined, f"{sym} is not taken from the shared library"
+    needed = subprocess.run(["ldd", exe], check=True, capture_output=True, text=True).stdout
+    assert "librlcu_b200.so" in needed
