@@ -333,7 +333,8 @@ def run_single(args):
     traffic = NCU_DRAM_BYTES_PER_PARAM * P
 
     # ---- CPU restatement on this machine's cores (bounded sample)
-    cpu_rate, cpu_sec, cores = cpu_port_step_rate(1 << 25, 3, 1, threads=0)
+    cpu_sample, cpu_steps = 1 << 26, 5
+    cpu_rate, cpu_sec, cores = cpu_port_step_rate(cpu_sample, cpu_steps, 1, threads=0)
     cpu_rate_1t, _, _ = cpu_port_step_rate(1 << 22, 2, 1, threads=1)
 
     line = {
@@ -356,7 +357,7 @@ def run_single(args):
         "gpu_launches": 2 * K,
         "clocks": clocks.report(),
         "cpu_baseline": {"value": cpu_rate, "unit": "params/s", "cores": cores, "kind": "port",
-                         "sample": f"{1 << 25} parameters per step, 3 steps, statistics + clip + update, "
+                         "sample": f"{cpu_sample} parameters per step, {cpu_steps} steps, statistics + clip + update, "
                                    f"OpenMP over all host threads; single thread: {cpu_rate_1t:.3e} params/s"},
     }
     if ref_cuda is not None:
