@@ -539,13 +539,19 @@ def run_sharded(args):
     if rank == 0:
         peak, peak_kind = measured_peak()
         link = 770.0                                   # measured peer copy, GB/s per direction per GPU
+        link_bidir = 641.0                             # same copy with both directions busy (--probe-links)
         wire = 2.0 * P * (world - 1) / world           # bytes each GPU sends (and receives) per collective
         upd_bytes = BYTES_PER_PARAM * S
+        def floor_for(rate):
+            if mode == pkg.ZERO1_P2P:
+                # both exchanges ride inside a kernel; each is bounded by the slower of its HBM
+                # traffic and the bytes it moves over NVLink
+                return (max(wire / (rate * 1e9), 4.0 * S / (peak * 1e9)) +
+                        max(wire / (rate * 1e9), upd_bytes / (peak * 1e9))) * 1e3
+            return (2 * wire / (rate * 1e9) + (upd_bytes + 2 * S) / (peak * 1e9)) * 1e3
+
+        floor_ms, floor_bidir_ms = floor_for(link), floor_for(link_bidir)
         if mode == pkg.ZERO1_P2P:
-            # both exchanges ride inside a kernel; each is bounded by the slower of its HBM
-            # traffic and the bytes it moves over NVLink
-            floor_ms = (max(wire / (link * 1e9), 4.0 * S / (peak * 1e9)) +
-                        max(wire / (link * 1e9), upd_bytes / (peak * 1e9))) * 1e3
             link_rates = {"reduce_scatter_statistics_fused": wire / (phase_ms["reduce_scatter_statistics_fused"] * 1e-3) / 1e9,
                           "update_allgather_fused": wire / (phase_ms["update_allgather_fused"] * 1e-3) / 1e9}
             upd_ms = phase_ms["update_allgather_fused"]
@@ -556,7 +562,6 @@ def run_sharded(args):
                     "frac": link_rates["update_allgather_fused"] / link,
                     "hbm_gbs": upd_bytes / (upd_ms * 1e-3) / 1e9, "traffic": NCU_DRAM_BYTES_PER_PARAM * S}
         else:
-            floor_ms = (2 * wire / (link * 1e9) + (upd_bytes + 2 * S) / (peak * 1e9)) * 1e3
             link_rates = {"reduce_scatter": wire / (phase_ms["reduce_scatter"] * 1e-3) / 1e9,
                           "all_gather": wire / (phase_ms["all_gather"] * 1e-3) / 1e9}
             roof = {"bound": "hbm", "kernel": "adamw_table_kernel (shard)",
@@ -581,7 +586,9 @@ def run_sharded(args):
             "link_gbs_per_direction": link_rates,
             "roofline": roof,
             "nvlink_roofline": {"floor_ms": floor_ms, "frac": floor_ms / ms_per_step,
-                                "what": "two exchanges of (N-1)/N x 2 bytes/param per GPU per direction at 770 GB/s and the shard's HBM traffic at the measured peak; overlapped inside the fused kernels in p2p mode, back to back in nccl mode"},
+                                "floor_ms_both_directions_busy": floor_bidir_ms,
+                                "frac_both_directions_busy": floor_bidir_ms / ms_per_step,
+                                "what": "two exchanges of (N-1)/N x 2 bytes/param per GPU per direction at 770 GB/s (one-direction peer copy) and the shard's HBM traffic at the measured peak; overlapped inside the fused kernels in p2p mode, back to back in nccl mode.  Both exchanges load both directions of every link at once, where the same peer copy reaches 641 GB/s per direction (bench.py --probe-links): the second pair of figures uses that rate"},
             "e2e": {"value": P / (e2e_ms * 1e-3), "unit": "params/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 2 * padded * world, "d2h_bytes_per_step": 64 * world,
                     "what": "each rank copies its FP16 gradient replica from pinned host memory, runs the sharded step, reads the record back"},
@@ -592,6 +599,40 @@ def run_sharded(args):
     z.close()
     dist.barrier()
     dist.destroy_process_group()
+
+
+def probe_links(args):
+    """Copy-engine bandwidth between GPU 0 and GPU 1 of this box, one direction alone and both
+    directions at once (one process, two devices, cudaMemcpyPeerAsync through torch).  The
+    sharded step keeps both directions busy, so the second figure is the ceiling that applies
+    to it."""
+    import torch
+    assert torch.cuda.device_count() >= 2, "needs two visible GPUs"
+    n = 596_049_920
+    a0, b0 = (torch.empty(n, dtype=torch.float16, device="cuda:0") for _ in range(2))
+    a1, b1 = (torch.empty(n, dtype=torch.float16, device="cuda:1") for _ in range(2))
+    s0, s1 = torch.cuda.Stream(device=0), torch.cuda.Stream(device=1)
+
+    def one_way():
+        with torch.cuda.device(0), torch.cuda.stream(s0):
+            b1.copy_(a0, non_blocking=True)
+
+    def two_way():
+        one_way()
+        with torch.cuda.device(1), torch.cuda.stream(s1):
+            b0.copy_(a1, non_blocking=True)
+
+    out = {}
+    for name, fn in (("one_direction", one_way), ("both_directions", two_way)):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(0), torch.cuda.synchronize(1)
+        t0 = time.perf_counter()
+        for _ in range(10):
+            fn()
+        torch.cuda.synchronize(0), torch.cuda.synchronize(1)
+        out[name] = 2 * n / ((time.perf_counter() - t0) / 10) / 1e9
+    print(json.dumps({"probe": "peer copy, GB/s per direction", **out}), flush=True)
 
 
 def main():
@@ -609,7 +650,12 @@ def main():
                     help="N=1: run the update through the cp.async.bulk variant of the kernel")
     ap.add_argument("--quick", action="store_true",
                     help="device-resident timing only (no end-to-end, CPU or reference-kernel legs): for profiler runs")
+    ap.add_argument("--probe-links", action="store_true",
+                    help="measure copy-engine peer bandwidth between GPU 0 and 1 (one and both directions) and exit")
     args = ap.parse_args()
+    if args.probe_links:
+        probe_links(args)
+        return
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference_arm(args)
