@@ -539,7 +539,6 @@ def run_sharded(args):
     if rank == 0:
         peak, peak_kind = measured_peak()
         link = 770.0                                   # measured peer copy, GB/s per direction per GPU
-        link_bidir = 641.0                             # same copy with both directions busy (--probe-links)
         wire = 2.0 * P * (world - 1) / world           # bytes each GPU sends (and receives) per collective
         upd_bytes = BYTES_PER_PARAM * S
         def floor_for(rate):
@@ -550,7 +549,7 @@ def run_sharded(args):
                         max(wire / (rate * 1e9), upd_bytes / (peak * 1e9))) * 1e3
             return (2 * wire / (rate * 1e9) + (upd_bytes + 2 * S) / (peak * 1e9)) * 1e3
 
-        floor_ms, floor_bidir_ms = floor_for(link), floor_for(link_bidir)
+        floor_ms = floor_for(link)
         if mode == pkg.ZERO1_P2P:
             link_rates = {"reduce_scatter_statistics_fused": wire / (phase_ms["reduce_scatter_statistics_fused"] * 1e-3) / 1e9,
                           "update_allgather_fused": wire / (phase_ms["update_allgather_fused"] * 1e-3) / 1e9}
@@ -586,9 +585,7 @@ def run_sharded(args):
             "link_gbs_per_direction": link_rates,
             "roofline": roof,
             "nvlink_roofline": {"floor_ms": floor_ms, "frac": floor_ms / ms_per_step,
-                                "floor_ms_both_directions_busy": floor_bidir_ms,
-                                "frac_both_directions_busy": floor_bidir_ms / ms_per_step,
-                                "what": "two exchanges of (N-1)/N x 2 bytes/param per GPU per direction at 770 GB/s (one-direction peer copy) and the shard's HBM traffic at the measured peak; overlapped inside the fused kernels in p2p mode, back to back in nccl mode.  Both exchanges load both directions of every link at once, where the same peer copy reaches 641 GB/s per direction (bench.py --probe-links): the second pair of figures uses that rate"},
+                                "what": "two exchanges of (N-1)/N x 2 bytes/param per GPU per direction at 770 GB/s (one-direction peer copy) and the shard's HBM traffic at the measured peak; overlapped inside the fused kernels in p2p mode, back to back in nccl mode"},
             "e2e": {"value": P / (e2e_ms * 1e-3), "unit": "params/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 2 * padded * world, "d2h_bytes_per_step": 64 * world,
                     "what": "each rank copies its FP16 gradient replica from pinned host memory, runs the sharded step, reads the record back"},
@@ -603,9 +600,8 @@ def run_sharded(args):
 
 def probe_links(args):
     """Copy-engine bandwidth between GPU 0 and GPU 1 of this box, one direction alone and both
-    directions at once (one process, two devices, cudaMemcpyPeerAsync through torch).  The
-    sharded step keeps both directions busy, so the second figure is the ceiling that applies
-    to it."""
+    directions at once (one process, two devices, cudaMemcpyPeerAsync through torch): what the
+    NVLink figures of the sharded step are compared with."""
     import torch
     assert torch.cuda.device_count() >= 2, "needs two visible GPUs"
     n = 596_049_920
