@@ -447,7 +447,7 @@ def run_sharded(args):
         return pkg.Zero1(box[0], rank, world, p_pool.data_ptr(), g_pool.data_ptr(), segments,
                          m_sh.data_ptr(), v_sh.data_ptr(), None, mode=mode)
 
-    mode = {"p2p": pkg.ZERO1_P2P, "ce": pkg.ZERO1_COPY_ENGINE, "nccl": pkg.ZERO1_NCCL}[args.zero1_mode]
+    mode = pkg.ZERO1_P2P if args.zero1_mode == "p2p" else pkg.ZERO1_NCCL
     mode_note = None
     try:
         z = create(mode)
@@ -455,7 +455,7 @@ def run_sharded(args):
         # Peer mapping needs pools that came from cudaMalloc (CUDA IPC); it fails on every rank
         # alike, e.g. under an allocator that uses virtual-memory segments.  The NCCL exchange
         # still runs the same kernels and is reported as what it is.
-        if mode == pkg.ZERO1_NCCL:
+        if mode != pkg.ZERO1_P2P:
             raise
         mode_note = f"peer-to-peer exchange unavailable ({exc}); ran the NCCL exchange"
         mode = pkg.ZERO1_NCCL
@@ -509,8 +509,7 @@ def run_sharded(args):
     z.poll_error()
     final = pkg.Stat.from_buffer_copy(stat.cpu().numpy().tobytes())
     ks = max(3, min(K, 10))
-    peer_mapped = mode != pkg.ZERO1_NCCL
-    if peer_mapped:
+    if mode == pkg.ZERO1_P2P:
         phase_ms = {"reduce_scatter_statistics_fused": timed(1, ks), "allreduce_finalize": timed(2, ks),
                     "update_allgather_fused": timed(4, ks)}
     else:
@@ -543,7 +542,7 @@ def run_sharded(args):
         wire = 2.0 * P * (world - 1) / world           # bytes each GPU sends (and receives) per collective
         upd_bytes = BYTES_PER_PARAM * S
         def floor_for(rate):
-            if peer_mapped:
+            if mode == pkg.ZERO1_P2P:
                 # both exchanges ride inside a kernel; each is bounded by the slower of its HBM
                 # traffic and the bytes it moves over NVLink
                 return (max(wire / (rate * 1e9), 4.0 * S / (peak * 1e9)) +
@@ -551,7 +550,7 @@ def run_sharded(args):
             return (2 * wire / (rate * 1e9) + (upd_bytes + 2 * S) / (peak * 1e9)) * 1e3
 
         floor_ms = floor_for(link)
-        if peer_mapped:
+        if mode == pkg.ZERO1_P2P:
             link_rates = {"reduce_scatter_statistics_fused": wire / (phase_ms["reduce_scatter_statistics_fused"] * 1e-3) / 1e9,
                           "update_allgather_fused": wire / (phase_ms["update_allgather_fused"] * 1e-3) / 1e9}
             upd_ms = phase_ms["update_allgather_fused"]
@@ -577,9 +576,6 @@ def run_sharded(args):
             "config": {"workload": workload_name(args), "params": P, "shard_params": S,
                        "exchange": ("peer-to-peer kernels over NVLink: fused reduce-scatter+statistics, fused update+all-gather, "
                                     "8-byte NCCL all-reduces for ordering and the norm") if mode == pkg.ZERO1_P2P else
-                                   ("copy engines over NVLink, chunked: pull of the peers' gradients overlapped with the "
-                                    "reduce+statistics kernel, push of new parameters overlapped with the update kernel, "
-                                    "8-byte NCCL all-reduces for ordering and the norm") if mode == pkg.ZERO1_COPY_ENGINE else
                                    "ncclReduceScatter(sum, f16) + ncclAllReduce(1 double) + ncclAllGather(f16)",
                        "l2": "each rank streams its whole 1.2 GB gradient and parameter pools per step, far larger than L2",
                        "grad_restore": "device copy of the rank's gradient replica before each step, outside the timed intervals",
@@ -593,7 +589,7 @@ def run_sharded(args):
             "e2e": {"value": P / (e2e_ms * 1e-3), "unit": "params/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 2 * padded * world, "d2h_bytes_per_step": 64 * world,
                     "what": "each rank copies its FP16 gradient replica from pinned host memory, runs the sharded step, reads the record back"},
-            "gpu_launches": (9 if mode == pkg.ZERO1_COPY_ENGINE else 3) * K * world,
+            "gpu_launches": (3 if mode == pkg.ZERO1_P2P else 3) * K * world,
             "clocks": clocks.report(),
         }
         print(json.dumps(line), flush=True)
@@ -642,8 +638,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="qwen3-0.6b", choices=["qwen3-0.6b", "qwen3-8b", "qwen3-0.6b-4l", "ragged-20k", "ragged-600"])
-    ap.add_argument("--zero1-mode", default="p2p", choices=["p2p", "ce", "nccl"],
-                    help="N>1: fused peer-to-peer kernels (default), copy-engine exchange, or NCCL collectives")
+    ap.add_argument("--zero1-mode", default="p2p", choices=["p2p", "nccl"],
+                    help="N>1: fused peer-to-peer kernels (default) or NCCL reduce-scatter/all-gather")
     ap.add_argument("--align", type=int, default=8,
                     help="N=1: elements every tensor start is aligned to inside the pools (8 = 16 bytes)")
     ap.add_argument("--bulk", action="store_true",

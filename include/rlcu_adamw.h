@@ -270,19 +270,11 @@ typedef struct rlcu_zero1_plan {
 /* how the two exchanges of the step are carried out */
 enum {
     RLCU_ZERO1_NCCL = 0,  /* ncclReduceScatter / ncclAllGather around the single-GPU kernels    */
-    RLCU_ZERO1_P2P = 1,   /* fused: the statistics kernel pulls every rank's gradients over
+    RLCU_ZERO1_P2P = 1    /* fused: the statistics kernel pulls every rank's gradients over
                              NVLink through peer-mapped pointers (FP32 sum in rank order, one
                              rounding), the update kernel pushes each new FP16 parameter into
                              every peer's pool.  One process per GPU, pools from cudaMalloc,
                              at most 8 ranks.  Rank ordering uses 8-byte NCCL collectives.      */
-    RLCU_ZERO1_COPY_ENGINE = 2
-                          /* same mapping, but the bytes cross NVLink on the copy engines, which
-                             move ~765 GB/s per direction where SM-issued traffic reaches ~640:
-                             the shard is cut into chunks; peers' gradient contributions are
-                             pulled into a local staging area ((world-1) x shard, allocated at
-                             create) while earlier chunks are summed (FP32, rank order, one
-                             rounding) by the same kernel as in P2P mode, and updated chunks are
-                             pushed to the peers while later chunks are updated.                 */
 };
 int rlcu_zero1_make_plan(const rlcu_zero1_segment* segs, uint64_t nsegs, int rank, int world,
                          rlcu_zero1_plan* out);

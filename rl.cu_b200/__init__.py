@@ -39,7 +39,7 @@ EXPORTS = [
 ]
 UNIQUE_ID_BYTES = 128
 PHASE_REDUCE_SCATTER, PHASE_STATISTICS, PHASE_UPDATE, PHASE_ALL_GATHER = 1, 2, 4, 8
-ZERO1_NCCL, ZERO1_P2P, ZERO1_COPY_ENGINE = 0, 1, 2
+ZERO1_NCCL, ZERO1_P2P = 0, 1
 NOALLOC_MAX_ELEMS = 1 << 31
 # C++-linkage launchers with RL.cu's signatures (include/kernels/adamw.cuh)
 CXX_EXPORTS = [

@@ -91,20 +91,6 @@ int check_geometry(const rlcu_zero1_segment* segs, uint64_t nsegs, int rank, int
     return RLCU_OK;
 }
 
-// the segments (or parts of segments) inside [a0, b0), as pieces whose state offsets count
-// from `state_origin` (the first element of the owning rank's shard)
-void pieces_in_range(const rlcu_zero1_segment* segs, uint64_t nsegs, uint64_t a0, uint64_t b0,
-                     uint64_t state_origin, std::vector<Piece>* pieces) {
-    uint64_t begin = 0;
-    for (uint64_t k = 0; k < nsegs; k++) {
-        const uint64_t end = begin + segs[k].n;
-        const uint64_t a = begin > a0 ? begin : a0;
-        const uint64_t b = end < b0 ? end : b0;
-        if (a < b) pieces->push_back({a, a - state_origin, b - a, segs[k].weight_decay, segs[k].flags});
-        begin = end;
-    }
-}
-
 void make_plan(const rlcu_zero1_segment* segs, uint64_t nsegs, int rank, int world,
                rlcu_zero1_plan* plan, std::vector<Piece>* pieces) {
     uint64_t total = 0;
@@ -119,10 +105,18 @@ void make_plan(const rlcu_zero1_segment* segs, uint64_t nsegs, int rank, int wor
     const uint64_t hi = lo + shard;
     plan->lo = lo < total ? lo : total;
     plan->hi = hi < total ? hi : total;
-    std::vector<Piece> local;
-    pieces_in_range(segs, nsegs, plan->lo, plan->hi, lo, &local);
-    plan->pieces = local.size();
-    if (pieces) *pieces = local;
+    uint64_t count = 0, begin = 0;
+    for (uint64_t k = 0; k < nsegs; k++) {
+        const uint64_t end = begin + segs[k].n;
+        const uint64_t a = begin > plan->lo ? begin : plan->lo;
+        const uint64_t b = end < plan->hi ? end : plan->hi;
+        if (a < b) {
+            count++;
+            if (pieces) pieces->push_back({a, a - lo, b - a, segs[k].weight_decay, segs[k].flags});
+        }
+        begin = end;
+    }
+    plan->pieces = count;
 }
 
 }  // namespace
@@ -141,22 +135,6 @@ struct rlcu_zero1 {
     rlcu::PeerIn grads_in{};
     rlcu::PeerOut params_out{};
     std::vector<void*> mapped;     // what cudaIpcOpenMemHandle returned, to be closed
-    // copy-engine mode: the shard is cut into chunks; peers' contributions are pulled into a
-    // local staging area by the copy engines while earlier chunks are being reduced, and new
-    // parameters are pushed out by the copy engines while later chunks are being updated
-    struct Chunk {
-        uint64_t lo = 0, n = 0;                 // element range inside the pools
-        rlcu_tensor_list* list = nullptr;
-        rlcu::PeerIn in{};                      // bases redirected into the staging area
-    };
-    std::vector<Chunk> chunks;
-    __half* staging = nullptr;                  // (world-1) slots of shard_elems halves
-    std::vector<int> peer_rank;                 // slot k holds rank peer_rank[k]
-    std::vector<cudaStream_t> copy_streams;     // one per peer
-    std::vector<cudaEvent_t> pulled;            // [peer][chunk]
-    std::vector<cudaEvent_t> updated;           // [chunk]
-    std::vector<cudaEvent_t> pushed;            // [peer]
-    cudaEvent_t start = nullptr;
 };
 
 namespace {
@@ -276,125 +254,6 @@ int setup_p2p(rlcu_zero1* z) {
     return RLCU_OK;
 }
 
-constexpr int kCopyChunks = 4;
-
-// Copy-engine mode on top of the peer mapping: chunk lists, staging area, streams, events.
-int setup_copy_engine(rlcu_zero1* z, const rlcu_zero1_segment* segs, uint64_t nsegs,
-                      float* m_shard, float* v_shard, float* master_shard) {
-    const int W = z->world;
-    const uint64_t S = z->plan.shard_elems;
-    const uint64_t shard_lo = S * (uint64_t)z->rank;
-    for (int j = 0; j < W; j++)
-        if (j != z->rank) z->peer_rank.push_back(j);
-    if (W > 1) RLCU_CUDA(cudaMalloc(&z->staging, (size_t)(W - 1) * S * sizeof(__half)));
-    uint64_t chunk = (S + kCopyChunks - 1) / kCopyChunks;
-    chunk = (chunk + kShardAlign - 1) / kShardAlign * kShardAlign;
-    for (uint64_t off = 0; off < S; off += chunk) {
-        rlcu_zero1::Chunk c;
-        c.lo = shard_lo + off;
-        c.n = (S - off) < chunk ? (S - off) : chunk;
-        std::vector<Piece> pieces;
-        pieces_in_range(segs, nsegs, c.lo < z->plan.total ? c.lo : z->plan.total,
-                        (c.lo + c.n) < z->plan.total ? (c.lo + c.n) : z->plan.total, shard_lo, &pieces);
-        std::vector<rlcu_tensor_desc> descs;
-        for (const Piece& p : pieces) {
-            rlcu_tensor_desc d{};
-            d.param = static_cast<char*>(z->param_pool) + p.pool_offset * 2;
-            d.grad = static_cast<const char*>(z->grad_pool) + p.pool_offset * 2;
-            d.m = m_shard + p.state_offset;
-            d.v = v_shard + p.state_offset;
-            d.master = master_shard ? master_shard + p.state_offset : nullptr;
-            d.n = p.n;
-            d.weight_decay = p.wd;
-            d.dtype = RLCU_F16;
-            d.flags = p.flags;
-            descs.push_back(d);
-        }
-        const int rc = rlcu_tensor_list_create(descs.data(), descs.size(), &c.list);
-        if (rc) return rc;
-        // the reduce kernel adds a pool offset to every base: point each peer's base so that
-        // pool offset `shard_lo` falls on the first element of that peer's staging slot
-        c.in.n = W;
-        c.in.local_base = static_cast<const __half*>(z->grad_pool);
-        for (int j = 0, k = 0; j < W; j++) {
-            if (j == z->rank) c.in.base[j] = static_cast<const __half*>(z->grad_pool);
-            else c.in.base[j] = z->staging + (size_t)(k++) * S - shard_lo;
-        }
-        z->chunks.push_back(c);
-    }
-    const size_t C = z->chunks.size(), P = z->peer_rank.size();
-    z->copy_streams.resize(P);
-    z->pulled.resize(P * C);
-    z->updated.resize(C);
-    z->pushed.resize(P);
-    for (auto& st : z->copy_streams) RLCU_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
-    for (auto& e : z->pulled) RLCU_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
-    for (auto& e : z->updated) RLCU_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
-    for (auto& e : z->pushed) RLCU_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
-    RLCU_CUDA(cudaEventCreateWithFlags(&z->start, cudaEventDisableTiming));
-    return RLCU_OK;
-}
-
-void release_copy_engine(rlcu_zero1* z) {
-    for (auto& c : z->chunks) rlcu_tensor_list_destroy(c.list);
-    z->chunks.clear();
-    for (auto st : z->copy_streams) if (st) cudaStreamDestroy(st);
-    for (auto e : z->pulled) if (e) cudaEventDestroy(e);
-    for (auto e : z->updated) if (e) cudaEventDestroy(e);
-    for (auto e : z->pushed) if (e) cudaEventDestroy(e);
-    if (z->start) cudaEventDestroy(z->start);
-    if (z->staging) cudaFree(z->staging);
-    z->copy_streams.clear(); z->pulled.clear(); z->updated.clear(); z->pushed.clear();
-    z->start = nullptr;
-    z->staging = nullptr;
-}
-
-// Reduce-scatter + statistics with the copy engines pulling: chunk c of every peer's
-// contribution lands in staging while chunk c-1 is being summed.
-int ce_reduce(rlcu_zero1* z, float unscale, rlcu_scaler_state* scaler, rlcu_stat* stat, cudaStream_t s) {
-    const size_t C = z->chunks.size(), P = z->peer_rank.size();
-    const uint64_t S = z->plan.shard_elems, shard_lo = S * (uint64_t)z->rank;
-    RLCU_CUDA(cudaEventRecord(z->start, s));
-    for (size_t k = 0; k < P; k++) {
-        RLCU_CUDA(cudaStreamWaitEvent(z->copy_streams[k], z->start, 0));
-        const __half* src_pool = z->grads_in.base[z->peer_rank[k]];
-        for (size_t c = 0; c < C; c++) {
-            const rlcu_zero1::Chunk& ch = z->chunks[c];
-            RLCU_CUDA(cudaMemcpyAsync(z->staging + k * S + (ch.lo - shard_lo), src_pool + ch.lo,
-                                      ch.n * sizeof(__half), cudaMemcpyDeviceToDevice, z->copy_streams[k]));
-            RLCU_CUDA(cudaEventRecord(z->pulled[k * C + c], z->copy_streams[k]));
-        }
-    }
-    for (size_t c = 0; c < C; c++) {
-        for (size_t k = 0; k < P; k++) RLCU_CUDA(cudaStreamWaitEvent(s, z->pulled[k * C + c], 0));
-        const int rc = rlcu::launch_reduce_stat(z->chunks[c].list, z->chunks[c].in, unscale, scaler, stat, c != 0, s);
-        if (rc) return rc;
-    }
-    return RLCU_OK;
-}
-
-// Update + all-gather with the copy engines pushing: chunk c of the new parameters goes out
-// to every peer while chunk c+1 is being updated.
-int ce_update(rlcu_zero1* z, const rlcu_hparams* hp, const rlcu_stat* stat, uint32_t step_flags, cudaStream_t s) {
-    const size_t C = z->chunks.size(), P = z->peer_rank.size();
-    for (size_t c = 0; c < C; c++) {
-        const rlcu_zero1::Chunk& ch = z->chunks[c];
-        const int rc = rlcu_adamw_multi_step(ch.list, hp, stat, step_flags, s);
-        if (rc) return rc;
-        RLCU_CUDA(cudaEventRecord(z->updated[c], s));
-        for (size_t k = 0; k < P; k++) {
-            RLCU_CUDA(cudaStreamWaitEvent(z->copy_streams[k], z->updated[c], 0));
-            RLCU_CUDA(cudaMemcpyAsync(z->params_out.base[k] + ch.lo, static_cast<const __half*>(z->param_pool) + ch.lo,
-                                      ch.n * sizeof(__half), cudaMemcpyDeviceToDevice, z->copy_streams[k]));
-        }
-    }
-    for (size_t k = 0; k < P; k++) {
-        RLCU_CUDA(cudaEventRecord(z->pushed[k], z->copy_streams[k]));
-        RLCU_CUDA(cudaStreamWaitEvent(s, z->pushed[k], 0));
-    }
-    return RLCU_OK;
-}
-
 void release_p2p(rlcu_zero1* z) {
     for (void* p : z->mapped) cudaIpcCloseMemHandle(p);
     z->mapped.clear();
@@ -449,8 +308,7 @@ int rlcu_zero1_create(const void* unique_id, int rank, int world,
                       float* m_shard, float* v_shard, float* master_shard,
                       uint32_t mode, rlcu_zero1** out) {
     if (!out) return set_error(RLCU_ERR_INVALID, "null out");
-    if (mode != RLCU_ZERO1_NCCL && mode != RLCU_ZERO1_P2P && mode != RLCU_ZERO1_COPY_ENGINE)
-        return set_error(RLCU_ERR_INVALID, "unknown mode %u", mode);
+    if (mode != RLCU_ZERO1_NCCL && mode != RLCU_ZERO1_P2P) return set_error(RLCU_ERR_INVALID, "unknown mode %u", mode);
     *out = nullptr;
     if (!unique_id || !param_pool || !grad_pool || !m_shard || !v_shard)
         return set_error(RLCU_ERR_INVALID, "null pointer");
@@ -502,12 +360,9 @@ int rlcu_zero1_create(const void* unique_id, int rank, int world,
         delete z;
         return set_error(RLCU_ERR_NCCL, "ncclCommInitRank: %s", api->GetErrorString(nr));
     }
-    if (mode == RLCU_ZERO1_P2P || mode == RLCU_ZERO1_COPY_ENGINE) {
+    if (mode == RLCU_ZERO1_P2P) {
         rc = setup_p2p(z);
-        if (!rc && mode == RLCU_ZERO1_COPY_ENGINE)
-            rc = setup_copy_engine(z, segs, nsegs, m_shard, v_shard, master_shard);
         if (rc) {
-            release_copy_engine(z);
             release_p2p(z);
             api->CommAbort(z->comm);
             rlcu_tensor_list_destroy(z->list);
@@ -532,28 +387,6 @@ int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float 
     // ones to the division); 1/world goes into the factor applied in registers
     const float unscale_all = unscale / (float)z->world;
     int rc;
-    if (z->mode == RLCU_ZERO1_COPY_ENGINE) {
-        if (step_flags & RLCU_STEP_ZERO_GRADS)
-            return set_error(RLCU_ERR_UNSUPPORTED, "RLCU_STEP_ZERO_GRADS is not available in the sharded step");
-        if (phases & 1u) {
-            rc = barrier(z, s);                  // every rank's gradients are complete
-            if (rc) return rc;
-            rc = ce_reduce(z, unscale_all, scaler, stat, s);
-            if (rc) return rc;
-        }
-        if (phases & 2u) {
-            RLCU_NCCL(z->api, z->api->AllReduce(&stat->sum_sq, &stat->sum_sq, 1, ncclDouble, ncclSum, z->comm, s));
-            rc = rlcu_gradstat_finalize(stat, unscale_all, max_norm, scaler, s);
-            if (rc) return rc;
-        }
-        if (phases & (4u | 8u)) {
-            rc = ce_update(z, hp, stat, step_flags, s);
-            if (rc) return rc;
-            rc = barrier(z, s);                  // every rank's pushes into my pool have landed
-            if (rc) return rc;
-        }
-        return RLCU_OK;
-    }
     if (z->mode == RLCU_ZERO1_P2P) {
         if (step_flags & RLCU_STEP_ZERO_GRADS)
             return set_error(RLCU_ERR_UNSUPPORTED, "RLCU_STEP_ZERO_GRADS is not available in the sharded step");
@@ -561,7 +394,7 @@ int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float 
             // every rank's gradients are complete before anyone reads them remotely
             rc = barrier(z, s);
             if (rc) return rc;
-            rc = rlcu::launch_reduce_stat(z->list, z->grads_in, unscale_all, scaler, stat, false, s);
+            rc = rlcu::launch_reduce_stat(z->list, z->grads_in, unscale_all, scaler, stat, s);
             if (rc) return rc;
         }
         if (phases & 2u) {
@@ -613,7 +446,6 @@ int rlcu_zero1_destroy(rlcu_zero1* z, int abort) {
         ncclResult_t nr = abort ? z->api->CommAbort(z->comm) : z->api->CommDestroy(z->comm);
         if (nr != ncclSuccess) rc = set_error(RLCU_ERR_NCCL, "communicator teardown: %s", z->api->GetErrorString(nr));
     }
-    release_copy_engine(z);
     release_p2p(z);
     const int rc2 = rlcu_tensor_list_destroy(z->list);
     delete z;

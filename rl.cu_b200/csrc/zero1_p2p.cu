@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(kThreads)
 reduce_stat_kernel(const WorkItem* __restrict__ table, uint32_t n_items,
                    const __grid_constant__ PeerIn peers, float unscale_arg,
                    const rlcu_scaler_state* scaler, rlcu_stat* out, float* partials,
-                   unsigned int* counter, int accumulate) {
+                   unsigned int* counter) {
     __shared__ float warp_sums[kThreads / 32];
     __shared__ bool is_last;
     float unscale = unscale_arg;
@@ -182,9 +182,7 @@ reduce_stat_kernel(const WorkItem* __restrict__ table, uint32_t n_items,
         for (int mask = 16; mask >= 1; mask >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, mask);
         if (threadIdx.x == 0) {
             *counter = 0;
-            // this rank's share (or, when the shard is reduced in several launches, a
-            // running total over them); the host code all-reduces it
-            out->sum_sq = accumulate ? out->sum_sq + s : s;
+            out->sum_sq = s;      // this rank's share; the host code all-reduces it
         }
     }
 }
@@ -244,8 +242,7 @@ int geometry(Geometry* out) {
 }  // namespace
 
 int launch_reduce_stat(rlcu_tensor_list* list, const PeerIn& peers, float unscale,
-                       const rlcu_scaler_state* scaler, rlcu_stat* stat, bool accumulate,
-                       cudaStream_t stream) {
+                       const rlcu_scaler_state* scaler, rlcu_stat* stat, cudaStream_t stream) {
     if (!list || !stat) return set_error(RLCU_ERR_INVALID, "null list or stat");
     if (peers.n < 1 || peers.n > kMaxWorld) return set_error(RLCU_ERR_INVALID, "world size %d not supported", peers.n);
     Geometry g;
@@ -259,7 +256,7 @@ int launch_reduce_stat(rlcu_tensor_list* list, const PeerIn& peers, float unscal
 #define RLCU_LAUNCH_REDUCE(W)                                                                   \
     reduce_stat_kernel<W><<<grid, kThreads, 0, stream>>>(list->d_items, list->n_items, peers,   \
                                                          unscale, scaler, stat, list->d_partials, \
-                                                         list->d_counter, accumulate ? 1 : 0)
+                                                         list->d_counter)
     switch (peers.n) {
         case 1: RLCU_LAUNCH_REDUCE(1); break;
         case 2: RLCU_LAUNCH_REDUCE(2); break;

@@ -20,13 +20,10 @@ struct PeerIn {
     const __half* base[kMaxWorld];
 };
 
-// Fused reduce-scatter + statistics over the elements of `list` (this rank's shard or a
-// part of it); writes the sum of squares to stat->sum_sq, or adds to it with `accumulate`.
-// The entries of peers.base need not be other GPUs' memory: a base may be offset so that
-// base + pool offset lands in a local staging copy of a peer's data.
+// Fused reduce-scatter + statistics over this rank's shard; writes the rank's
+// share of the sum of squares to stat->sum_sq.
 int launch_reduce_stat(rlcu_tensor_list* list, const PeerIn& peers, float unscale,
-                       const rlcu_scaler_state* scaler, rlcu_stat* stat, bool accumulate,
-                       cudaStream_t stream);
+                       const rlcu_scaler_state* scaler, rlcu_stat* stat, cudaStream_t stream);
 
 // Fused update + all-gather: the update pass with every new FP16 parameter also
 // stored into the peers' pools.

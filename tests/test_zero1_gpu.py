@@ -83,7 +83,7 @@ def _check(pkg, O, world, outs, use_master, mode=0):
     for r, o in enumerate(outs):
         lo, hi = o["lo"], min(o["lo"] + S, total)
         g_sum[lo:hi] = o["g"][lo:hi]
-    if world <= 2 or mode >= 1:
+    if world <= 2 or mode == 1:
         # two ranks: one correctly rounded addition; peer-to-peer mode: FP32 sum, one rounding
         assert np.array_equal(g_sum, exact)
     else:
@@ -118,7 +118,7 @@ def _check(pkg, O, world, outs, use_master, mode=0):
         assert not o["p"][total:].any()              # padding stays zero
 
 
-@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("mode", [0, 1])
 @pytest.mark.parametrize("use_master", [False, True])
 def test_world_one_equals_unsharded_step(pkg, O, use_master, mode):
     import torch
@@ -148,7 +148,7 @@ def _worker(rank, world, port, out_dir, use_master, mode):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", [0, 1, 2], ids=["nccl", "p2p", "ce"])
+@pytest.mark.parametrize("mode", [0, 1], ids=["nccl", "p2p"])
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_sharded_step_on_several_gpus(pkg, O, tmp_path, world, mode):
     import torch
@@ -218,7 +218,7 @@ def test_rank_leaving_between_steps_is_handled_on_the_host(pkg, O, tmp_path):
     assert np.array_equal(a["p"], b["p"])                  # and both hold the same parameters
 
 
-@pytest.mark.parametrize("mode", [0, 1, 2], ids=["nccl", "p2p", "ce"])
+@pytest.mark.parametrize("mode", [0, 1], ids=["nccl", "p2p"])
 def test_sharded_step_with_device_scaler_skips_on_overflow(pkg, O, mode):
     """Loss scaling through the sharded step (world 1 here): the scaler's grad_mul carries
     1/world, a non-finite gradient makes every rank skip and halve the scale, a clean step
@@ -341,7 +341,7 @@ def _overflow_worker(rank, world, port, out_dir, mode):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", [0, 1, 2], ids=["nccl", "p2p", "ce"])
+@pytest.mark.parametrize("mode", [0, 1], ids=["nccl", "p2p"])
 def test_overflow_in_one_replica_skips_every_rank(pkg, O, tmp_path, mode):
     """A non-finite gradient in one rank's replica reaches every rank through the reduced sum of
     squares: all ranks skip, all halve the scale; the next clean step equals the oracle."""
