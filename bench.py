@@ -180,7 +180,10 @@ def cpu_port_step_rate(sample_params, steps, warmup, threads=0):
              g=O.f2h(rng.standard_normal(n, dtype=np.float32) * np.float32(1e-4 * (596_049_920 / n) ** 0.5)),
              m=np.zeros(n, np.float32), v=np.zeros(n, np.float32), wd=0.01)
     ts = O.make_tensors([e])
-    cores = os.cpu_count() if threads == 0 else threads
+    # an explicit thread count: launchers such as torch.distributed.run export OMP_NUM_THREADS=1
+    if threads == 0:
+        threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    cores = threads
     times = []
     for i in range(warmup + steps):
         t = 6 + i
