@@ -224,6 +224,22 @@ __device__ __forceinline__ WorkItem load_item(const WorkItem* table, uint32_t id
     return it;
 }
 
+// What a skipped (overflowed) step still does when RLCU_STEP_ZERO_GRADS is set: the stale
+// gradients are cleared, parameters and moments stay untouched.
+__device__ __forceinline__ void clear_gradients(const WorkItem* table, uint32_t n_items) {
+    for (uint32_t idx = blockIdx.x; idx < n_items; idx += gridDim.x) {
+        const WorkItem it = load_item(table, idx);
+        if (it.flags & (RLCU_TENSOR_NORM_ONLY | RLCU_TENSOR_GRAD_ZERO)) continue;
+        if ((it.flags & kItemKindMask) == kItemKindF32) {
+            float* g = const_cast<float*>(static_cast<const float*>(it.g));
+            for (uint32_t i = threadIdx.x; i < it.count; i += blockDim.x) g[i] = 0.0f;
+        } else {
+            __half* g = const_cast<__half*>(static_cast<const __half*>(it.g));
+            for (uint32_t i = threadIdx.x; i < it.count; i += blockDim.x) g[i] = __float2half_rn(0.0f);
+        }
+    }
+}
+
 // Resolves the per-launch constants from the statistics record (if any).
 // Returns false when the step must be skipped.
 __device__ __forceinline__ bool resolve_step(const rlcu_stat* stat, uint32_t step_flags,

@@ -7,13 +7,16 @@
 //                     device memory.  Replaces RL.cu's sum_sq_* kernels, its
 //                     blocking read-back and host sqrtf
 //                     (include/training/trainer.h:103-133, 324-344).
-//   adamw_kernel    : one persistent launch over a table of work items that
+//   adamw_table_kernel : one persistent launch over a table of work items that
 //                     covers every tensor; reads p/g/m/v (12 B/param) and
 //                     writes p/m/v (10 B/param).  Replaces RL.cu's three
 //                     launch_adamw_* calls and its two scale kernels
 //                     (include/training/optimizer.h:119-147,
 //                      src/kernels/adamw.cu, trainer.h:136-145, 345-349).
-// Both are pure streaming kernels bound by HBM bandwidth: CUDA cores only,
+//                     adamw_table_bulk_kernel is the same pass with the traffic
+//                     issued by cp.async.bulk; adamw_flat_kernel serves the
+//                     single-tensor entry points.
+// All are pure streaming kernels bound by HBM bandwidth: CUDA cores only,
 // 128/256-bit coalesced accesses, grids sized to the SM count.
 #include "rlcu_adamw.h"
 
@@ -48,17 +51,7 @@ adamw_table_kernel(const WorkItem* __restrict__ table, uint32_t n_items, StepCon
         // overflowed step: parameters and moments stay as they are; stale
         // gradients are still cleared if the caller asked for that
         if (!(step_flags & RLCU_STEP_ZERO_GRADS)) return;
-        for (uint32_t idx = blockIdx.x; idx < n_items; idx += gridDim.x) {
-            const WorkItem it = load_item(table, idx);
-            if (it.flags & (RLCU_TENSOR_NORM_ONLY | RLCU_TENSOR_GRAD_ZERO)) continue;
-            if ((it.flags & kItemKindMask) == kItemKindF32) {
-                float* g = const_cast<float*>(static_cast<const float*>(it.g));
-                for (uint32_t i = threadIdx.x; i < it.count; i += kThreads) g[i] = 0.0f;
-            } else {
-                __half* g = const_cast<__half*>(static_cast<const __half*>(it.g));
-                for (uint32_t i = threadIdx.x; i < it.count; i += kThreads) g[i] = __float2half_rn(0.0f);
-            }
-        }
+        clear_gradients(table, n_items);
         return;
     }
     uint32_t idx = blockIdx.x;
@@ -88,17 +81,7 @@ adamw_table_bulk_kernel(const WorkItem* __restrict__ table, uint32_t n_items, St
     GradXform xf;
     if (!resolve_step(stat, step_flags, c, xf)) {
         if (!(step_flags & RLCU_STEP_ZERO_GRADS)) return;
-        for (uint32_t idx = blockIdx.x; idx < n_items; idx += gridDim.x) {
-            const WorkItem it = load_item(table, idx);
-            if (it.flags & (RLCU_TENSOR_NORM_ONLY | RLCU_TENSOR_GRAD_ZERO)) continue;
-            if ((it.flags & kItemKindMask) == kItemKindF32) {
-                float* g = const_cast<float*>(static_cast<const float*>(it.g));
-                for (uint32_t i = threadIdx.x; i < it.count; i += blockDim.x) g[i] = 0.0f;
-            } else {
-                __half* g = const_cast<__half*>(static_cast<const __half*>(it.g));
-                for (uint32_t i = threadIdx.x; i < it.count; i += blockDim.x) g[i] = __float2half_rn(0.0f);
-            }
-        }
+        clear_gradients(table, n_items);
         return;
     }
     if (threadIdx.x == 0) {

@@ -555,3 +555,26 @@ def test_step_replays_from_a_cuda_graph(pkg, O, torch):
     for da, db in zip(dev_a, dev_b):
         for k in da:
             assert np.array_equal(da[k].get().view(np.uint8), db[k].get().view(np.uint8)), k
+
+
+@pytest.mark.parametrize("bulk", [False, True])
+def test_skipped_step_still_clears_gradients_when_asked(pkg, O, torch, bulk):
+    specs = [(8192 * 2 + 5, "h", 0.01, 0), (900, "f", 0.0, 0), (8192, "hm", 0.0, pkg.TENSOR_GRAD_ZERO)]
+    host, dev, descs = make_case(O, torch, pkg, specs, seed=101)
+    g = host[0]["g"].copy()
+    g[77] = 0x7C00
+    dev[0]["g"].set(g)
+    frozen_grad = dev[2]["g"].get()
+    before = [{k: b.get() for k, b in d.items() if k != "g"} for d in dev]
+    tl = pkg.TensorList(descs)
+    stat = torch.zeros(16, device="cuda")
+    tl.gradstat(stat.data_ptr(), 1.0, 1.0)
+    tl.step(pkg.hparams(1e-3, 0.9, 0.999, 1e-8, 1), stat.data_ptr(),
+            pkg.STEP_ZERO_GRADS | (pkg.STEP_BULK_COPY if bulk else 0))
+    tl.check()
+    assert read_stat(pkg, stat).found_inf == 1
+    for d, b in zip(dev, before):
+        for k in b:
+            assert np.array_equal(d[k].get().view(np.uint8), b[k].view(np.uint8)), k
+    assert not dev[0]["g"].get().any() and not dev[1]["g"].get().any()
+    assert np.array_equal(dev[2]["g"].get(), frozen_grad)      # a GRAD_ZERO tensor's buffer is never touched
