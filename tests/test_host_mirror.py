@@ -84,3 +84,32 @@ def test_reference_test_binary_links_against_the_library(pkg, tmp_path):
         assert sym in undefined, f"{sym} is not taken from the shared library"
     needed = subprocess.run(["ldd", exe], check=True, capture_output=True, text=True).stdout
     assert "librlcu_b200.so" in needed
+
+
+@pytest.fixture(scope="module")
+def zero1_threads_binary(pkg, tmp_path_factory):
+    if shutil.which("nvcc") is None:
+        pytest.skip("nvcc not available")
+    out = str(tmp_path_factory.mktemp("zero1") / "test_zero1_threads")
+    lib_dir = os.path.join(ROOT, "rl.cu_b200", "lib")
+    cmd = NVCC + ["-I", os.path.join(ROOT, "include"), os.path.join(CPP, "test_zero1_threads.cu"), "-o", out,
+                  "-L", lib_dir, "-lrlcu_b200", "-Xlinker", f"-rpath={lib_dir}", "-Xcompiler", "-pthread"]
+    subprocess.run(cmd, check=True)
+    return out
+
+
+def test_cxx_sharded_driver_builds(zero1_threads_binary):
+    """The C ABI of the sharded step is usable from plain C++ (no Python, no PyTorch)."""
+    assert os.path.exists(zero1_threads_binary)
+
+
+@pytest.mark.gpu
+def test_cxx_sharded_driver_runs_on_several_gpus(zero1_threads_binary):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([zero1_threads_binary], capture_output=True, text=True, env=env, timeout=600)
+    print(r.stdout, r.stderr[-2000:])
+    assert r.returncode == 0, r.stdout + r.stderr[-2000:]
+    assert "[FAIL]" not in r.stdout and r.stdout.count("[PASS]") == 4
