@@ -207,7 +207,7 @@ def run_reference_arm(args):
         "impl": "reference", "metric": "adamw_params_per_sec", "value": rate, "unit": "params/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
-        "dtype": "f16 params/grads, f32 moments", "data": "synthetic",
+        "dtype": "f32", "storage": "f16 params and grads, f32 moments", "data": "synthetic",
         "config": {"workload": workload_name(args), "sample_params": sample},
         "cpu_baseline": {"value": rate, "unit": "params/s", "cores": cores, "kind": "port",
                          "sample": f"{sample} parameters of the workload per step (statistics + clip + update), "
@@ -343,7 +343,7 @@ def run_single(args):
     line = {
         "metric": "adamw_params_per_sec", "value": value, "unit": "params/s", "n_gpus": 1,
         "steps": K, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16 params/grads, f32 moments and math",
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "storage": "f16 params and grads, f32 moments",
         "data": "synthetic",
         "config": {"workload": workload_name(args), "params": P, "tensors": len(shapes),
                    "launches_per_step": 2, "l2": "working set 7.2 GB per step, far larger than the 126 MB L2",
@@ -575,7 +575,7 @@ def run_sharded(args):
             "metric": "adamw_params_per_sec", "value": P / (ms_per_step * 1e-3), "unit": "params/s",
             "n_gpus": world, "steps": K, "warmup": args.warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f16 params/grads, f32 moments and math", "data": "synthetic",
+            "dtype": "f32", "storage": "f16 params and grads, f32 moments", "data": "synthetic",
             "config": {"workload": workload_name(args), "params": P, "shard_params": S,
                        "exchange": ("peer-to-peer kernels over NVLink: fused reduce-scatter+statistics, fused update+all-gather, "
                                     "8-byte NCCL all-reduces for ordering and the norm") if mode == pkg.ZERO1_P2P else
