@@ -237,7 +237,7 @@ int rlcu_adamw_multi_step(rlcu_tensor_list* list, const rlcu_hparams* hp,
 /* No counterpart in RL.cu (single GPU, no NCCL).  One process (or host thread) per
  * GPU.  All parameters live in one flat FP16 pool and all gradients in another
  * (RL.cu's fp16_pool / half_pool layout, include/model/weights.h:43-61), both
- * padded to rlcu_zero1_padded_elems().  The flat element space is cut into
+ * padded to rlcu_zero1_plan.padded_elems.  The flat element space is cut into
  * `world` equal contiguous shards; rank r keeps m / v (/ master) for shard r only.
  * One step:
  *   reduce-scatter (sum) of the FP16 gradients, in place       NCCL over NVLink
@@ -299,7 +299,9 @@ int rlcu_zero1_create(const void* unique_id, int rank, int world,
                       uint32_t mode, rlcu_zero1** out);
 /* One sharded optimizer step, enqueued on `stream` (no host synchronisation).
  * `unscale` is 1/loss_scale (1 without loss scaling); the division by `world` is
- * added inside.  `stat` is a device record that receives the global norm etc.
+ * added inside.  With a `scaler` the factor is taken from it instead
+ * (grad_mul/scale): set its grad_mul to 1/world.  `stat` is a device record that
+ * receives the global norm etc.
  * phases: bit mask for measurements, 0 = all.  NCCL mode: 1 reduce-scatter, 2
  * statistics + all-reduce, 4 update, 8 all-gather.  P2P mode: 1 fused
  * reduce-scatter + statistics, 2 all-reduce + finalize, 4 (or 8) fused update +
