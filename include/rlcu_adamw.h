@@ -14,7 +14,7 @@
  *     caller and must not alias each other.
  *   - `stream` is a cudaStream_t passed as void* so that this header needs no
  *     CUDA headers; NULL is the legacy default stream, which is what RL.cu uses.
- *   - FP16 data is IEEE binary16 (`__half`), passed as void*.
+ *   - FP16 data is IEEE binary16 (`__half`), BF16 data is bfloat16; both are passed as void*.
  *   - Sizes are 64-bit element counts.  RL.cu's `int n` launchers are kept
  *     separately in include/kernels/adamw.cuh for source compatibility.
  *   - There is no CPU fallback: without a CUDA device every compute entry
@@ -42,8 +42,10 @@ enum {
     RLCU_ERR_UNSUPPORTED = 5
 };
 
-/* element kinds */
-enum { RLCU_F16 = 0, RLCU_F32 = 1 };
+/* element kinds.  RL.cu trains in FP16 (RLCU_F16) with FP32 norm weights (RLCU_F32).
+ * RLCU_BF16 (bfloat16 parameters and gradients, same arithmetic in FP32, same options)
+ * has no counterpart in RL.cu; its results are checked against the CPU restatement only. */
+enum { RLCU_F16 = 0, RLCU_F32 = 1, RLCU_BF16 = 2 };
 
 /* per-tensor flags */
 enum {
@@ -58,8 +60,9 @@ enum {
 /* flags of the update pass */
 enum {
     RLCU_STEP_ROUND_CLIP_FP16 = 1u, /* when the clip is active, round g*coef to FP16
-                                       before use, as RL.cu's scale_half_kernel
-                                       stores it (trainer.h:136-139). FP16 tensors only. */
+                                       (BF16 for BF16 tensors) before use, as RL.cu's
+                                       scale_half_kernel stores it (trainer.h:136-139).
+                                       FP32 tensors are scaled in FP32.                   */
     RLCU_STEP_DEVICE_BIAS_CORRECTION = 2u, /* take 1-beta^t from the statistics record
                                        (written by the statistics pass when a device-side
                                        scaler state is attached) instead of rlcu_hparams */
@@ -81,16 +84,16 @@ enum {
  * from Qwen3Weights / Qwen3Gradients (weights.h:43-61, qwen3.h:190-218), m / v /
  * master from AdamWOptimizer's state (optimizer.h:150-156). 64 bytes. */
 typedef struct rlcu_tensor_desc {
-    void*       param;        /* __half* or float* by dtype; updated in place         */
+    void*       param;        /* __half*, bfloat16* or float* by dtype; updated in place */
     const void* grad;         /* same kind as param; may be NULL with GRAD_ZERO        */
     float*      m;            /* first moment                                          */
     float*      v;            /* second moment                                         */
-    float*      master;       /* FP32 master copy (F16 only) or NULL.  With a master,
+    float*      master;       /* FP32 master copy (F16/BF16 only) or NULL.  With a master,
                                  param is write-only, as in launch_adamw_fp16.         */
     uint64_t    n;            /* elements                                              */
     float       weight_decay; /* decoupled; RL.cu uses 0 for embedding and norms
                                  (optimizer.h:131-146)                                 */
-    uint32_t    dtype;        /* RLCU_F16 / RLCU_F32                                   */
+    uint32_t    dtype;        /* RLCU_F16 / RLCU_F32 / RLCU_BF16                       */
     uint32_t    flags;        /* RLCU_TENSOR_*                                         */
     uint32_t    reserved;     /* must be 0                                             */
 } rlcu_tensor_desc;
@@ -153,6 +156,15 @@ int rlcu_adamw_fp16_master(float* master_w, void* model_w, const void* grad, flo
 /* Same arithmetic without a master copy: the weight is read from the FP16
  * parameter (12 bytes read + 10 written per element).  No RL.cu counterpart. */
 int rlcu_adamw_fp16(void* param, const void* grad, float* m, float* v,
+                    int64_t n, float lr, float beta1, float beta2, float eps,
+                    float weight_decay, float bias_correction1, float bias_correction2,
+                    void* stream);
+/* The two calls above for bfloat16 parameters and gradients (no RL.cu counterpart). */
+int rlcu_adamw_bf16_master(float* master_w, void* model_w, const void* grad, float* m, float* v,
+                           int64_t n, float lr, float beta1, float beta2, float eps,
+                           float weight_decay, float bias_correction1, float bias_correction2,
+                           void* stream);
+int rlcu_adamw_bf16(void* param, const void* grad, float* m, float* v,
                     int64_t n, float lr, float beta1, float beta2, float eps,
                     float weight_decay, float bias_correction1, float bias_correction2,
                     void* stream);

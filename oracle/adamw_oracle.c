@@ -67,6 +67,22 @@ void orc_h2f_array(const uint16_t* src, float* dst, int64_t n) {
     for (int64_t i = 0; i < n; i++) dst[i] = orc_h2f(src[i]);
 }
 
+float orc_bf2f(uint16_t b) { return bits_f32((uint32_t)b << 16); }
+
+uint16_t orc_f2bf(float f) {
+    uint32_t x = f32_bits(f);
+    if ((x & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)0x7FFFu;      /* NaN, as __float2bfloat16_rn */
+    x += 0x7FFFu + ((x >> 16) & 1u);                                    /* round to nearest even */
+    return (uint16_t)(x >> 16);
+}
+
+void orc_f2bf_array(const float* src, uint16_t* dst, int64_t n) {
+    for (int64_t i = 0; i < n; i++) dst[i] = orc_f2bf(src[i]);
+}
+void orc_bf2f_array(const uint16_t* src, float* dst, int64_t n) {
+    for (int64_t i = 0; i < n; i++) dst[i] = orc_bf2f(src[i]);
+}
+
 /* ------------------------------------------------------------------ */
 /* the element update                                                  */
 /* ------------------------------------------------------------------ */
@@ -168,6 +184,18 @@ double orc_sum_sq_half(const uint16_t* g, int64_t n, float unscale, int threads)
     return s;
 }
 
+double orc_sum_sq_bf16(const uint16_t* g, int64_t n, float unscale, int threads) {
+    double s = 0.0;
+    int nt = pick_threads(threads);
+    #pragma omp parallel for num_threads(nt) schedule(static) reduction(+:s)
+    for (int64_t i = 0; i < n; i++) {
+        float x = orc_bf2f(g[i]) * unscale;
+        float sq = x * x;
+        if (isfinite(sq)) s += (double)sq;
+    }
+    return s;
+}
+
 double orc_sum_sq_float(const float* g, int64_t n, float unscale, int threads) {
     double s = 0.0;
     int nt = pick_threads(threads);
@@ -247,6 +275,10 @@ void orc_gradstat(const orc_tensor* t, uint64_t count, float unscale, float max_
         if (t[k].dtype == ORC_F16) {
             s += orc_sum_sq_half((const uint16_t*)t[k].grad, (int64_t)t[k].n, unscale, threads);
             inf |= orc_count_nonfinite_half((const uint16_t*)t[k].grad, (int64_t)t[k].n) != 0;
+        } else if (t[k].dtype == ORC_BF16) {
+            const uint16_t* g = (const uint16_t*)t[k].grad;
+            s += orc_sum_sq_bf16(g, (int64_t)t[k].n, unscale, threads);
+            for (uint64_t i = 0; i < t[k].n; i++) inf |= (g[i] & 0x7F80u) == 0x7F80u;
         } else {
             s += orc_sum_sq_float((const float*)t[k].grad, (int64_t)t[k].n, unscale, threads);
             inf |= orc_count_nonfinite_float((const float*)t[k].grad, (int64_t)t[k].n) != 0;
@@ -272,17 +304,18 @@ int orc_multi_step(const orc_tensor* t, uint64_t count, const orc_hparams* hp,
                           hp->bias_correction1, hp->bias_correction2);
         int zero = (d->flags & ORC_FLAG_GRAD_ZERO) != 0;
         int64_t n = (int64_t)d->n;
-        if (d->dtype == ORC_F16) {
+        if (d->dtype == ORC_F16 || d->dtype == ORC_BF16) {
+            const int bf = d->dtype == ORC_BF16;
             uint16_t* p = (uint16_t*)d->param;
             const uint16_t* g = (const uint16_t*)d->grad;
             #pragma omp parallel for num_threads(nt) schedule(static)
             for (int64_t i = 0; i < n; i++) {
-                float x = zero ? 0.0f : orc_h2f(g[i]) * coef;
-                if (round_clip) x = orc_h2f(orc_f2h(x));   /* trainer.h:138 */
-                float w0 = d->master ? d->master[i] : orc_h2f(p[i]);
+                float x = zero ? 0.0f : (bf ? orc_bf2f(g[i]) : orc_h2f(g[i])) * coef;
+                if (round_clip) x = bf ? orc_bf2f(orc_f2bf(x)) : orc_h2f(orc_f2h(x));   /* trainer.h:138 */
+                float w0 = d->master ? d->master[i] : (bf ? orc_bf2f(p[i]) : orc_h2f(p[i]));
                 float w = upd(w0, x, &d->m[i], &d->v[i], &kk, rounding);
                 if (d->master) d->master[i] = w;
-                p[i] = orc_f2h(w);
+                p[i] = bf ? orc_f2bf(w) : orc_f2h(w);
             }
         } else {
             float* p = (float*)d->param;

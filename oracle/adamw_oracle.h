@@ -52,7 +52,7 @@ extern "C" {
 enum { ORC_UNFUSED = 0, ORC_NVCC = ORC_ROUNDING(2, 2, 0, 0) };
 
 /* element kinds and flags; binary-compatible with rlcu_tensor_desc */
-enum { ORC_F16 = 0, ORC_F32 = 1 };
+enum { ORC_F16 = 0, ORC_F32 = 1, ORC_BF16 = 2 };   /* BF16: no reference counterpart, parity unpinned */
 enum { ORC_FLAG_NORM_ONLY = 1u, ORC_FLAG_GRAD_ZERO = 2u };
 enum { ORC_STEP_ROUND_CLIP_FP16 = 1u };
 
@@ -95,6 +95,11 @@ uint16_t orc_f2h(float f);
 float    orc_h2f(uint16_t h);
 void     orc_f2h_array(const float* src, uint16_t* dst, int64_t n);
 void     orc_h2f_array(const uint16_t* src, float* dst, int64_t n);
+/* bfloat16 <-> binary32, round-to-nearest-even (NaN kept quiet) */
+uint16_t orc_f2bf(float f);
+float    orc_bf2f(uint16_t b);
+void     orc_f2bf_array(const float* src, uint16_t* dst, int64_t n);
+void     orc_bf2f_array(const uint16_t* src, float* dst, int64_t n);
 
 /* include/training/optimizer.h:121-122 */
 float orc_bias_correction(float beta, int step);
@@ -120,6 +125,7 @@ void orc_adamw_fp32(float* w, const float* grad, float* m, float* v, int64_t n,
  * FP32 atomic order is unspecified, so the oracle gives the exact sum). */
 double orc_sum_sq_half(const uint16_t* g, int64_t n, float unscale, int threads);
 double orc_sum_sq_float(const float* g, int64_t n, float unscale, int threads);
+double orc_sum_sq_bf16(const uint16_t* g, int64_t n, float unscale, int threads);
 int64_t orc_count_nonfinite_half(const uint16_t* g, int64_t n);
 int64_t orc_count_nonfinite_float(const float* g, int64_t n);
 /* include/training/trainer.h:136-145 */

@@ -28,7 +28,7 @@ def rounding(m_mode, v_mode, w_fused, d_fused):
 
 
 NVCC = rounding(2, 2, 0, 0)
-F16, F32 = 0, 1
+F16, F32, BF16 = 0, 1, 2
 FLAG_NORM_ONLY, FLAG_GRAD_ZERO = 1, 2
 STEP_ROUND_CLIP_FP16 = 1
 
@@ -75,6 +75,8 @@ def lib() -> C.CDLL:
         L.orc_h2f.argtypes, L.orc_h2f.restype = [C.c_uint16], f
         L.orc_f2h_array.argtypes = [vp, vp, i64]
         L.orc_h2f_array.argtypes = [vp, vp, i64]
+        L.orc_f2bf_array.argtypes = [vp, vp, i64]
+        L.orc_bf2f_array.argtypes = [vp, vp, i64]
         L.orc_bias_correction.argtypes, L.orc_bias_correction.restype = [f, i32], f
         L.orc_adamw_fp16_master.argtypes = [vp, vp, vp, vp, vp, i64] + hyper + [i32, i32]
         L.orc_adamw_fp16.argtypes = [vp, vp, vp, vp, i64] + hyper + [i32, i32]
@@ -114,6 +116,20 @@ def h2f(h: np.ndarray) -> np.ndarray:
     h = np.ascontiguousarray(h, dtype=np.uint16)
     out = np.empty(h.shape, dtype=np.float32)
     lib().orc_h2f_array(_p(h), _p(out), h.size)
+    return out
+
+
+def f2bf(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(x.shape, dtype=np.uint16)
+    lib().orc_f2bf_array(_p(x), _p(out), x.size)
+    return out
+
+
+def bf2f(b: np.ndarray) -> np.ndarray:
+    b = np.ascontiguousarray(b, dtype=np.uint16)
+    out = np.empty(b.shape, dtype=np.float32)
+    lib().orc_bf2f_array(_p(b), _p(out), b.size)
     return out
 
 
@@ -161,7 +177,7 @@ def make_tensors(entries) -> C.Array:
         t.master = _p(e.get("master"))
         t.n = p.size if p is not None else e["g"].size
         t.weight_decay = e.get("wd", 0.0)
-        t.dtype = F16 if (p if p is not None else e["g"]).dtype == np.uint16 else F32
+        t.dtype = e.get("dtype", F16 if (p if p is not None else e["g"]).dtype == np.uint16 else F32)
         t.flags = e.get("flags", 0)
     return arr
 

@@ -21,7 +21,7 @@ CSRC = os.path.join(_HERE, "csrc")
 LIB_PATH = os.path.join(_HERE, "lib", "librlcu_b200.so")
 
 OK, ERR_INVALID, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_UNSUPPORTED = range(6)
-F16, F32 = 0, 1
+F16, F32, BF16 = 0, 1, 2
 TENSOR_NORM_ONLY, TENSOR_GRAD_ZERO = 1, 2
 STEP_ROUND_CLIP_FP16, STEP_DEVICE_BIAS_CORRECTION, STEP_ZERO_GRADS, STEP_BULK_COPY = 1, 2, 4, 8
 STAT_PARTIAL = 1
@@ -29,7 +29,7 @@ STAT_PARTIAL = 1
 # every symbol include/rlcu_adamw.h declares
 EXPORTS = [
     "rlcu_abi_version", "rlcu_last_error", "rlcu_adamw_fp16_master", "rlcu_adamw_fp16",
-    "rlcu_adamw_fp32", "rlcu_half_to_float", "rlcu_tensor_list_create",
+    "rlcu_adamw_bf16_master", "rlcu_adamw_bf16", "rlcu_adamw_fp32", "rlcu_half_to_float", "rlcu_tensor_list_create",
     "rlcu_tensor_list_destroy", "rlcu_tensor_list_check", "rlcu_selftest_bounded_wait", "rlcu_tensor_list_numel", "rlcu_tensor_list_stat_numel",
     "rlcu_tensor_list_work_items", "rlcu_gradstat", "rlcu_gradstat_finalize",
     "rlcu_adamw_multi_step", "rlcu_bias_correction", "rlcu_gradstat_flat_noalloc",
@@ -134,6 +134,8 @@ def lib() -> C.CDLL:
     L.rlcu_adamw_fp16_master.argtypes = [vp, vp, vp, vp, vp, i64] + hyper + [vp]
     L.rlcu_adamw_fp16.argtypes = [vp, vp, vp, vp, i64] + hyper + [vp]
     L.rlcu_adamw_fp32.argtypes = [vp, vp, vp, vp, i64] + hyper + [vp]
+    L.rlcu_adamw_bf16_master.argtypes = [vp, vp, vp, vp, vp, i64] + hyper + [vp]
+    L.rlcu_adamw_bf16.argtypes = [vp, vp, vp, vp, i64] + hyper + [vp]
     L.rlcu_half_to_float.argtypes = [vp, vp, i64, vp]
     L.rlcu_tensor_list_create.argtypes = [vp, u64, C.POINTER(vp)]
     L.rlcu_tensor_list_destroy.argtypes = [vp]
@@ -183,6 +185,14 @@ def adamw_fp16_master(master, model_w, grad, m, v, n, lr, beta1, beta2, eps, wd,
 
 def adamw_fp16(param, grad, m, v, n, lr, beta1, beta2, eps, wd, bc1, bc2, stream=None):
     check(lib().rlcu_adamw_fp16(param, grad, m, v, n, lr, beta1, beta2, eps, wd, bc1, bc2, stream))
+
+
+def adamw_bf16_master(master, model_w, grad, m, v, n, lr, beta1, beta2, eps, wd, bc1, bc2, stream=None):
+    check(lib().rlcu_adamw_bf16_master(master, model_w, grad, m, v, n, lr, beta1, beta2, eps, wd, bc1, bc2, stream))
+
+
+def adamw_bf16(param, grad, m, v, n, lr, beta1, beta2, eps, wd, bc1, bc2, stream=None):
+    check(lib().rlcu_adamw_bf16(param, grad, m, v, n, lr, beta1, beta2, eps, wd, bc1, bc2, stream))
 
 
 def adamw_fp32(w, grad, m, v, n, lr, beta1, beta2, eps, wd, bc1, bc2, stream=None):

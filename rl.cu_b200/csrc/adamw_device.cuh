@@ -2,6 +2,7 @@
 // accesses, FP16 packing, the AdamW element update and the block reduction.
 #pragma once
 
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -34,6 +35,7 @@ constexpr uint32_t kItemKindF16Master = 1u << 8;
 constexpr uint32_t kItemKindF32 = 2u << 8;
 constexpr uint32_t kItemVec16 = 1u << 10;       // every pointer 16-byte aligned
 constexpr uint32_t kItemVec32 = 1u << 11;       // FP32 pointers 32-byte aligned too
+constexpr uint32_t kItemBF16 = 1u << 12;        // the 16-bit data of an F16-kind item is bfloat16
 
 // One unit of work: at most kChunk consecutive elements of one tensor, with
 // every pointer already advanced to the first of them.  64 bytes so that a
@@ -144,6 +146,39 @@ __device__ __forceinline__ uint4 f8_to_h8(const F8& r) {
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// bfloat16 twins of the two packers above
+__device__ __forceinline__ F8 b8_to_f8(uint4 x) {
+    F8 r;
+    const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        r.a[2 * i] = __uint_as_float(w[i] << 16);            // bfloat16 is the top half of an FP32
+        r.a[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+    return r;
+}
+
+__device__ __forceinline__ uint4 f8_to_b8(const F8& r) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(r.a[2 * i], r.a[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+__device__ __forceinline__ F8 x8_to_f8(uint4 x, bool bf) { return bf ? b8_to_f8(x) : h8_to_f8(x); }
+__device__ __forceinline__ uint4 f8_to_x8(const F8& r, bool bf) { return bf ? f8_to_b8(r) : f8_to_h8(r); }
+
+// scalar forms on raw 16-bit patterns
+__device__ __forceinline__ float x_to_f(unsigned short bits, bool bf) {
+    return bf ? __uint_as_float((uint32_t)bits << 16) : __half2float(__ushort_as_half(bits));
+}
+__device__ __forceinline__ unsigned short f_to_x(float x, bool bf) {
+    return bf ? __bfloat16_as_ushort(__float2bfloat16_rn(x)) : __half_as_ushort(__float2half_rn(x));
+}
+
 // ---- arithmetic -------------------------------------------------------------
 // The AdamW element update of RL.cu (src/kernels/adamw.cu:25-36).  Every
 // operation is spelled with an explicit round-to-nearest intrinsic, in exactly
@@ -174,6 +209,10 @@ __device__ __forceinline__ float decay_factor(float lr, float wd) {
 // (include/training/trainer.h:136-139).
 __device__ __forceinline__ float round_through_half(float x) {
     return __half2float(__float2half_rn(x));
+}
+// the same for bfloat16 gradients
+__device__ __forceinline__ float round_through_16(float x, bool bf) {
+    return bf ? __bfloat162float(__float2bfloat16_rn(x)) : round_through_half(x);
 }
 
 // ---- reduction --------------------------------------------------------------

@@ -45,9 +45,9 @@ __device__ __forceinline__ void store_param_h(__half* dst, __half val, const Pee
 }
 
 template <bool ROUND>
-__device__ __forceinline__ float xform_h(float g, float coef) {
+__device__ __forceinline__ float xform_h(float g, float coef, bool bf) {
     float x = __fmul_rn(g, coef);
-    if constexpr (ROUND) x = round_through_half(x);
+    if constexpr (ROUND) x = round_through_16(x, bf);
     return x;
 }
 
@@ -60,6 +60,7 @@ __device__ __forceinline__ void f16_groups(const WorkItem& it, int first_group, 
     uint4 gw[U], pw[U];
     F8 m[U], v[U], w[U];
     const bool zero = (it.flags & RLCU_TENSOR_GRAD_ZERO) != 0;
+    const bool bf = (it.flags & kItemBF16) != 0;
 #pragma unroll
     for (int u = 0; u < U; u++) {
         const size_t e = (size_t)(first_group + u * group_stride) * kGroup;
@@ -72,17 +73,17 @@ __device__ __forceinline__ void f16_groups(const WorkItem& it, int first_group, 
 #pragma unroll
     for (int u = 0; u < U; u++) {
         const size_t e = (size_t)(first_group + u * group_stride) * kGroup;
-        F8 g = h8_to_f8(gw[u]);
-        if constexpr (KIND == 0) w[u] = h8_to_f8(pw[u]);
+        F8 g = x8_to_f8(gw[u], bf);
+        if constexpr (KIND == 0) w[u] = x8_to_f8(pw[u], bf);
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            const float x = xform_h<ROUND>(g.a[i], xf.coef);
+            const float x = xform_h<ROUND>(g.a[i], xf.coef, bf);
             w[u].a[i] = adamw_element(w[u].a[i], x, m[u].a[i], v[u].a[i], c, decay);
         }
         st_f8<V32>(it.m + e, m[u]);
         st_f8<V32>(it.v + e, v[u]);
         if constexpr (KIND == 1) st_f8<V32>(it.master + e, w[u]);
-        store_param_h8<PEERS>(static_cast<__half*>(it.p) + e, f8_to_h8(w[u]), peers);
+        store_param_h8<PEERS>(static_cast<__half*>(it.p) + e, f8_to_x8(w[u], bf), peers);
         if (xf.zero_grads && !zero)
             st_h8(const_cast<__half*>(static_cast<const __half*>(it.g)) + e, make_uint4(0, 0, 0, 0));
     }
@@ -145,12 +146,13 @@ __device__ __forceinline__ void scalar_range(const WorkItem& it, uint32_t begin,
         } else {
             __half* p = static_cast<__half*>(it.p);
             __half* g = const_cast<__half*>(static_cast<const __half*>(it.g));
-            float x = zero ? 0.0f : __fmul_rn(__half2float(g[i]), xf.coef);
-            if (xf.round_half) x = round_through_half(x);
-            const float w0 = (kind == kItemKindF16Master) ? it.master[i] : __half2float(p[i]);
+            const bool bf = (it.flags & kItemBF16) != 0;
+            float x = zero ? 0.0f : __fmul_rn(x_to_f(__half_as_ushort(g[i]), bf), xf.coef);
+            if (xf.round_half) x = round_through_16(x, bf);
+            const float w0 = (kind == kItemKindF16Master) ? it.master[i] : x_to_f(__half_as_ushort(p[i]), bf);
             const float w = adamw_element(w0, x, m, v, c, decay);
             if (kind == kItemKindF16Master) it.master[i] = w;
-            store_param_h<PEERS>(p + i, __float2half_rn(w), peers);
+            store_param_h<PEERS>(p + i, __ushort_as_half(f_to_x(w, bf)), peers);
             if (xf.zero_grads && !zero) g[i] = __float2half_rn(0.0f);
         }
         it.m[i] = m;

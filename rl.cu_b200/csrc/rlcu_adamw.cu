@@ -283,12 +283,11 @@ __device__ __forceinline__ float scaler_unscale(const rlcu_scaler_state* scaler)
     return __fmul_rn(mul, __fdiv_rn(1.0f, scaler->scale));
 }
 
-__device__ __forceinline__ void accum_h8(uint4 x, float unscale, float (&acc)[4]) {
-    const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+__device__ __forceinline__ void accum_h8(uint4 x, float unscale, float (&acc)[4], bool bf) {
+    const F8 f = x8_to_f8(x, bf);
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-        const float a = f.x * unscale, b = f.y * unscale;
+        const float a = f.a[2 * i] * unscale, b = f.a[2 * i + 1] * unscale;
         acc[i] = fmaf(a, a, acc[i]);
         acc[i] = fmaf(b, b, acc[i]);
     }
@@ -319,10 +318,11 @@ gradstat_kernel(const WorkItem* __restrict__ table, uint32_t n_items, float unsc
         const uint32_t fl = e.x;
         if (fl & RLCU_TENSOR_GRAD_ZERO) continue;
         const bool f32 = (fl & kItemKindMask) == kItemKindF32;
+        const bool bf = (fl & kItemBF16) != 0;
         if (!(fl & kItemVec16)) {
             for (uint32_t i = threadIdx.x; i < count; i += kThreads) {
                 const float x = (f32 ? static_cast<const float*>(g)[i]
-                                     : __half2float(static_cast<const __half*>(g)[i])) * unscale;
+                                     : x_to_f(static_cast<const unsigned short*>(g)[i], bf)) * unscale;
                 acc[0] = fmaf(x, x, acc[0]);
             }
         } else if (!f32) {
@@ -333,13 +333,13 @@ gradstat_kernel(const WorkItem* __restrict__ table, uint32_t n_items, float unsc
                 for (int u = 0; u < kGroupsPerThread; u++)
                     x[u] = ld_h8(gh + (size_t)(threadIdx.x + u * kThreads) * kGroup);
 #pragma unroll
-                for (int u = 0; u < kGroupsPerThread; u++) accum_h8(x[u], unscale, acc);
+                for (int u = 0; u < kGroupsPerThread; u++) accum_h8(x[u], unscale, acc, bf);
             } else {
                 const uint32_t groups = count / kGroup;
                 for (uint32_t grp = threadIdx.x; grp < groups; grp += kThreads)
-                    accum_h8(ld_h8(gh + (size_t)grp * kGroup), unscale, acc);
+                    accum_h8(ld_h8(gh + (size_t)grp * kGroup), unscale, acc, bf);
                 for (uint32_t i = groups * kGroup + threadIdx.x; i < count; i += kThreads) {
-                    const float x = __half2float(gh[i]) * unscale;
+                    const float x = x_to_f(__half_as_ushort(gh[i]), bf) * unscale;
                     acc[0] = fmaf(x, x, acc[0]);
                 }
             }
@@ -446,8 +446,8 @@ int classify(const rlcu_tensor_desc& d, uint32_t* bits) {
     if (d.dtype == RLCU_F32) {
         if (d.master) return set_error(RLCU_ERR_INVALID, "FP32 tensor with a master copy");
         kind = kItemKindF32;
-    } else if (d.dtype == RLCU_F16) {
-        kind = d.master ? kItemKindF16Master : kItemKindF16;
+    } else if (d.dtype == RLCU_F16 || d.dtype == RLCU_BF16) {
+        kind = (d.master ? kItemKindF16Master : kItemKindF16) | (d.dtype == RLCU_BF16 ? kItemBF16 : 0u);
     } else {
         return set_error(RLCU_ERR_INVALID, "unknown dtype %u", d.dtype);
     }
@@ -558,6 +558,23 @@ int rlcu_adamw_fp16(void* param, const void* grad, float* m, float* v,
     return launch_flat(d, n, lr, beta1, beta2, eps, bc1, bc2, stream);
 }
 
+int rlcu_adamw_bf16_master(float* master_w, void* model_w, const void* grad, float* m, float* v,
+                           int64_t n, float lr, float beta1, float beta2, float eps,
+                           float weight_decay, float bc1, float bc2, void* stream) {
+    if (n <= 0) return RLCU_OK;
+    if (!master_w) return set_error(RLCU_ERR_INVALID, "null master");
+    rlcu_tensor_desc d = {model_w, grad, m, v, master_w, (uint64_t)n, weight_decay, RLCU_BF16, 0, 0};
+    return launch_flat(d, n, lr, beta1, beta2, eps, bc1, bc2, stream);
+}
+
+int rlcu_adamw_bf16(void* param, const void* grad, float* m, float* v,
+                    int64_t n, float lr, float beta1, float beta2, float eps,
+                    float weight_decay, float bc1, float bc2, void* stream) {
+    if (n <= 0) return RLCU_OK;
+    rlcu_tensor_desc d = {param, grad, m, v, nullptr, (uint64_t)n, weight_decay, RLCU_BF16, 0, 0};
+    return launch_flat(d, n, lr, beta1, beta2, eps, bc1, bc2, stream);
+}
+
 int rlcu_adamw_fp32(float* w, const float* grad, float* m, float* v,
                     int64_t n, float lr, float beta1, float beta2, float eps,
                     float weight_decay, float bc1, float bc2, void* stream) {
@@ -620,7 +637,7 @@ int rlcu_tensor_list_create(const rlcu_tensor_desc* descs, uint64_t count, rlcu_
             it.master = d.master ? d.master + off : nullptr;
             it.count = (uint32_t)((d.n - off) < want ? (d.n - off) : want);
             it.wd = d.weight_decay;
-            it.flags = d.flags | (bits & kItemKindMask) | item_alignment(it, d);
+            it.flags = d.flags | (bits & (kItemKindMask | kItemBF16)) | item_alignment(it, d);
             items.push_back(it);
             off += it.count;
         }
