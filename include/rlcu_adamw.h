@@ -288,6 +288,8 @@ enum {
                              every peer's pool.  One process per GPU, pools from cudaMalloc,
                              at most 8 ranks.  Rank ordering uses 8-byte NCCL collectives.      */
 };
+/* OR this into `mode` when the two pools hold bfloat16 instead of FP16 */
+#define RLCU_ZERO1_POOLS_BF16 0x100u
 int rlcu_zero1_make_plan(const rlcu_zero1_segment* segs, uint64_t nsegs, int rank, int world,
                          rlcu_zero1_plan* out);
 /* The descriptors rank `rank` would update, with pointers expressed as element

@@ -126,6 +126,7 @@ struct rlcu_zero1 {
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1;
     uint32_t mode = RLCU_ZERO1_NCCL;
+    ncclDataType_t wire_type = ncclHalf;   // element type of the pools on the wire (NCCL mode)
     rlcu_zero1_plan plan{};
     void* param_pool = nullptr;
     void* grad_pool = nullptr;
@@ -308,6 +309,8 @@ int rlcu_zero1_create(const void* unique_id, int rank, int world,
                       float* m_shard, float* v_shard, float* master_shard,
                       uint32_t mode, rlcu_zero1** out) {
     if (!out) return set_error(RLCU_ERR_INVALID, "null out");
+    const bool bf16 = (mode & RLCU_ZERO1_POOLS_BF16) != 0;
+    mode &= ~(uint32_t)RLCU_ZERO1_POOLS_BF16;
     if (mode != RLCU_ZERO1_NCCL && mode != RLCU_ZERO1_P2P) return set_error(RLCU_ERR_INVALID, "unknown mode %u", mode);
     *out = nullptr;
     if (!unique_id || !param_pool || !grad_pool || !m_shard || !v_shard)
@@ -328,6 +331,7 @@ int rlcu_zero1_create(const void* unique_id, int rank, int world,
     z->rank = rank;
     z->world = world;
     z->mode = mode;
+    z->wire_type = bf16 ? ncclBfloat16 : ncclHalf;
     z->param_pool = param_pool;
     z->grad_pool = grad_pool;
     std::vector<Piece> pieces;
@@ -343,7 +347,7 @@ int rlcu_zero1_create(const void* unique_id, int rank, int world,
         d.master = master_shard ? master_shard + p.state_offset : nullptr;
         d.n = p.n;
         d.weight_decay = p.wd;
-        d.dtype = RLCU_F16;
+        d.dtype = bf16 ? RLCU_BF16 : RLCU_F16;
         d.flags = p.flags;
         descs.push_back(d);
     }
@@ -413,7 +417,7 @@ int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float 
         return RLCU_OK;
     }
     if (phases & 1u)
-        RLCU_NCCL(z->api, z->api->ReduceScatter(z->grad_pool, gshard, S, ncclHalf, ncclSum, z->comm, s));
+        RLCU_NCCL(z->api, z->api->ReduceScatter(z->grad_pool, gshard, S, z->wire_type, ncclSum, z->comm, s));
     if (phases & 2u) {
         rc = rlcu_gradstat(z->list, unscale_all, max_norm, scaler, stat, RLCU_STAT_PARTIAL, s);
         if (rc) return rc;
@@ -426,7 +430,7 @@ int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float 
         if (rc) return rc;
     }
     if (phases & 8u)
-        RLCU_NCCL(z->api, z->api->AllGather(pshard, z->param_pool, S, ncclHalf, z->comm, s));
+        RLCU_NCCL(z->api, z->api->AllGather(pshard, z->param_pool, S, z->wire_type, z->comm, s));
     return RLCU_OK;
 }
 

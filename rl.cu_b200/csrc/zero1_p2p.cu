@@ -24,8 +24,8 @@ namespace rlcu {
 
 namespace {
 
-__device__ __forceinline__ void add_h8(uint4 x, F8& acc) {
-    const F8 f = h8_to_f8(x);
+__device__ __forceinline__ void add_h8(uint4 x, F8& acc, bool bf) {
+    const F8 f = x8_to_f8(x, bf);
 #pragma unroll
     for (int i = 0; i < 8; i++) acc.a[i] = __fadd_rn(acc.a[i], f.a[i]);
 }
@@ -43,7 +43,7 @@ __device__ __forceinline__ void square_accumulate(const F8& x, float unscale, fl
 // once to FP16.  Group u of the thread is `stride` groups after group u-1.
 template <int WORLD, int UB>
 __device__ __forceinline__ void reduce_groups(const PeerIn& peers, ptrdiff_t off, __half* dst,
-                                              ptrdiff_t stride, float unscale, float (&acc)[4]) {
+                                              ptrdiff_t stride, float unscale, float (&acc)[4], bool bf) {
     constexpr int W = WORLD > 0 ? WORLD : kMaxWorld;
     const int n = WORLD > 0 ? WORLD : peers.n;
     uint4 x[UB][W];
@@ -54,13 +54,13 @@ __device__ __forceinline__ void reduce_groups(const PeerIn& peers, ptrdiff_t off
             if (j < n) x[u][j] = ld_h8(peers.base[j] + off + u * stride * kGroup);
 #pragma unroll
     for (int u = 0; u < UB; u++) {
-        F8 sum = h8_to_f8(x[u][0]);
+        F8 sum = x8_to_f8(x[u][0], bf);
 #pragma unroll
         for (int j = 1; j < W; j++)
-            if (j < n) add_h8(x[u][j], sum);
-        const uint4 r = f8_to_h8(sum);
+            if (j < n) add_h8(x[u][j], sum, bf);
+        const uint4 r = f8_to_x8(sum, bf);
         *reinterpret_cast<uint4*>(dst + u * stride * kGroup) = r;   // default policy: the update pass reads it next
-        square_accumulate(h8_to_f8(r), unscale, acc);
+        square_accumulate(x8_to_f8(r, bf), unscale, acc);
     }
 }
 
@@ -76,7 +76,7 @@ __device__ __forceinline__ U8 ld_h16(const __half* p) {
 // 16 consecutive elements per thread with 256-bit loads from every rank.
 template <int WORLD, int UB>
 __device__ __forceinline__ void reduce_wide(const PeerIn& peers, ptrdiff_t off, __half* dst,
-                                            ptrdiff_t stride, float unscale, float (&acc)[4]) {
+                                            ptrdiff_t stride, float unscale, float (&acc)[4], bool bf) {
     constexpr int W = WORLD > 0 ? WORLD : kMaxWorld;
     const int n = WORLD > 0 ? WORLD : peers.n;
     U8 x[UB][W];
@@ -89,13 +89,13 @@ __device__ __forceinline__ void reduce_wide(const PeerIn& peers, ptrdiff_t off, 
     for (int u = 0; u < UB; u++) {
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            F8 sum = h8_to_f8(make_uint4(x[u][0].w[4 * h], x[u][0].w[4 * h + 1], x[u][0].w[4 * h + 2], x[u][0].w[4 * h + 3]));
+            F8 sum = x8_to_f8(make_uint4(x[u][0].w[4 * h], x[u][0].w[4 * h + 1], x[u][0].w[4 * h + 2], x[u][0].w[4 * h + 3]), bf);
 #pragma unroll
             for (int j = 1; j < W; j++)
-                if (j < n) add_h8(make_uint4(x[u][j].w[4 * h], x[u][j].w[4 * h + 1], x[u][j].w[4 * h + 2], x[u][j].w[4 * h + 3]), sum);
-            const uint4 r = f8_to_h8(sum);
+                if (j < n) add_h8(make_uint4(x[u][j].w[4 * h], x[u][j].w[4 * h + 1], x[u][j].w[4 * h + 2], x[u][j].w[4 * h + 3]), sum, bf);
+            const uint4 r = f8_to_x8(sum, bf);
             *reinterpret_cast<uint4*>(dst + u * stride * 16 + h * 8) = r;
-            square_accumulate(h8_to_f8(r), unscale, acc);
+            square_accumulate(x8_to_f8(r, bf), unscale, acc);
         }
     }
 }
@@ -130,6 +130,7 @@ reduce_stat_kernel(const WorkItem* __restrict__ table, uint32_t n_items,
         const uint32_t count = d.z;
         const uint32_t fl = e.x;
         if (fl & RLCU_TENSOR_GRAD_ZERO) continue;
+        const bool bf = (fl & kItemBF16) != 0;
         const ptrdiff_t base_off = g - peers.local_base;
         const uint32_t groups = (fl & kItemVec16) ? count / kGroup : 0;
         // full items whose addresses are 32-byte aligned on every rank: 256-bit loads
@@ -142,7 +143,7 @@ reduce_stat_kernel(const WorkItem* __restrict__ table, uint32_t n_items,
 #pragma unroll
             for (int b = 0; b < 2 / UB; b++) {
                 const ptrdiff_t first = (ptrdiff_t)(threadIdx.x + b * UB * kThreads) * 16;
-                reduce_wide<WORLD, UB>(peers, base_off + first, g + first, kThreads, unscale, acc);
+                reduce_wide<WORLD, UB>(peers, base_off + first, g + first, kThreads, unscale, acc, bf);
             }
             continue;
         }
@@ -151,18 +152,18 @@ reduce_stat_kernel(const WorkItem* __restrict__ table, uint32_t n_items,
 #pragma unroll
             for (int b = 0; b < kGroupsPerThread / UB; b++) {
                 const ptrdiff_t first = (ptrdiff_t)(threadIdx.x + b * UB * kThreads) * kGroup;
-                reduce_groups<WORLD, UB>(peers, base_off + first, g + first, kThreads, unscale, acc);
+                reduce_groups<WORLD, UB>(peers, base_off + first, g + first, kThreads, unscale, acc, bf);
             }
             continue;
         }
         for (uint32_t grp = threadIdx.x; grp < groups; grp += kThreads)
-            reduce_groups<WORLD, 1>(peers, base_off + (ptrdiff_t)grp * kGroup, g + (size_t)grp * kGroup, 0, unscale, acc);
+            reduce_groups<WORLD, 1>(peers, base_off + (ptrdiff_t)grp * kGroup, g + (size_t)grp * kGroup, 0, unscale, acc, bf);
         for (uint32_t i = groups * kGroup + threadIdx.x; i < count; i += kThreads) {
-            float s = __half2float(peers.base[0][base_off + i]);
-            for (int j = 1; j < n; j++) s = __fadd_rn(s, __half2float(peers.base[j][base_off + i]));
-            const __half r = __float2half_rn(s);
+            float s = x_to_f(__half_as_ushort(peers.base[0][base_off + i]), bf);
+            for (int j = 1; j < n; j++) s = __fadd_rn(s, x_to_f(__half_as_ushort(peers.base[j][base_off + i]), bf));
+            const __half r = __ushort_as_half(f_to_x(s, bf));
             g[i] = r;
-            const float x = __half2float(r) * unscale;
+            const float x = x_to_f(__half_as_ushort(r), bf) * unscale;
             acc[0] = fmaf(x, x, acc[0]);
         }
     }

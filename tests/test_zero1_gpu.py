@@ -25,9 +25,16 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _inputs(O, world):
+def _inputs(O, world, bf=False):
     total = sum(s[0] for s in SEGS)
     rng = np.random.default_rng(200)
+    if bf:
+        p = O.f2bf(rng.standard_normal(total).astype(np.float32) * np.float32(0.02))
+        m = (rng.standard_normal(total) * 1e-3).astype(np.float32)
+        v = (rng.random(total) * 1e-5).astype(np.float32)
+        grads = [O.f2bf(np.random.default_rng([201, r]).standard_normal(total).astype(np.float32) * np.float32(5e-3))
+                 for r in range(world)]
+        return total, p, m, v, grads
     p = O.f2h(rng.standard_normal(total).astype(np.float32) * np.float32(0.02))
     m = (rng.standard_normal(total) * 1e-3).astype(np.float32)
     v = (rng.random(total) * 1e-5).astype(np.float32)
@@ -36,9 +43,9 @@ def _inputs(O, world):
     return total, p, m, v, grads
 
 
-def _run_rank(rank, world, uid, pkg, O, torch, use_master, mode=0):
+def _run_rank(rank, world, uid, pkg, O, torch, use_master, mode=0, bf=False):
     """Runs one sharded step on this process's GPU; returns host copies of everything."""
-    total, p, m, v, grads = _inputs(O, world)
+    total, p, m, v, grads = _inputs(O, world, bf)
     plan = pkg.zero1_plan(SEGS, rank, world)
     S, padded = int(plan.shard_elems), int(plan.padded_elems)
     lo = rank * S
@@ -55,10 +62,10 @@ def _run_rank(rank, world, uid, pkg, O, torch, use_master, mode=0):
 
     p_pool, g_pool = pool16(p), pool16(grads[rank])
     m_sh, v_sh = shard32(m), shard32(v)
-    master_sh = shard32(O.h2f(p)) if use_master else None
+    master_sh = shard32((O.bf2f if bf else O.h2f)(p)) if use_master else None
     stat = torch.zeros(16, device="cuda")
     z = pkg.Zero1(uid, rank, world, p_pool.data_ptr(), g_pool.data_ptr(), SEGS, m_sh.data_ptr(), v_sh.data_ptr(),
-                  master_sh.data_ptr() if use_master else None, mode=mode)
+                  master_sh.data_ptr() if use_master else None, mode=mode | (pkg.ZERO1_POOLS_BF16 if bf else 0))
     hp = pkg.hparams(LR, B1, B2, EPS, T)
     z.step(hp, stat.data_ptr(), 1.0, MAX_NORM, None, pkg.STEP_ROUND_CLIP_FP16)
     torch.cuda.synchronize()
@@ -71,14 +78,15 @@ def _run_rank(rank, world, uid, pkg, O, torch, use_master, mode=0):
     return out
 
 
-def _check(pkg, O, world, outs, use_master, mode=0):
-    total, p, m, v, grads = _inputs(O, world)
+def _check(pkg, O, world, outs, use_master, mode=0, bf=False):
+    total, p, m, v, grads = _inputs(O, world, bf)
+    to_f, to_16 = (O.bf2f, O.f2bf) if bf else (O.h2f, O.f2h)
     S = outs[0]["S"]
-    # (ii) the reduce-scattered shard against the FP32 sum (rank order) rounded once to FP16
-    acc = O.h2f(grads[0]).copy()
+    # (ii) the reduce-scattered shard against the FP32 sum (rank order) rounded once to 16 bits
+    acc = to_f(grads[0]).copy()
     for g in grads[1:]:
-        acc = acc + O.h2f(g)
-    exact = O.f2h(acc)
+        acc = acc + to_f(g)
+    exact = to_16(acc)
     g_sum = np.zeros(total, np.uint16)
     for r, o in enumerate(outs):
         lo, hi = o["lo"], min(o["lo"] + S, total)
@@ -89,13 +97,15 @@ def _check(pkg, O, world, outs, use_master, mode=0):
     else:
         # NCCL adds in FP16 hop by hop in an order of its choosing: each of the world-1
         # additions can lose half an FP16 ulp of the partial sum it produces
-        bound = (world - 1) * 2.0 ** -11 * np.sum([np.abs(O.h2f(g)) for g in grads], axis=0) + 2.0 ** -24
-        assert (np.abs(O.h2f(g_sum).astype(np.float64) - acc) <= bound).all()
+        ulp = 2.0 ** (-8 if bf else -11)
+        bound = (world - 1) * ulp * np.sum([np.abs(to_f(g)) for g in grads], axis=0) + 2.0 ** -24
+        assert (np.abs(to_f(g_sum).astype(np.float64) - acc) <= bound).all()
     # (i) single-rank oracle step on the summed gradients, unscale = 1/world
-    master = O.h2f(p)
+    master = to_f(p)
     entries, off = [], 0
     for n, wd, fl in SEGS:
-        e = dict(p=p[off:off + n], g=g_sum[off:off + n], m=m[off:off + n], v=v[off:off + n], wd=wd, flags=fl)
+        e = dict(p=p[off:off + n], g=g_sum[off:off + n], m=m[off:off + n], v=v[off:off + n], wd=wd, flags=fl,
+                 dtype=O.BF16 if bf else O.F16)
         if use_master:
             e["master"] = master[off:off + n]
         entries.append(e)
@@ -128,7 +138,15 @@ def test_world_one_equals_unsharded_step(pkg, O, use_master, mode):
     _check(pkg, O, 1, [out], use_master, mode)
 
 
-def _worker(rank, world, port, out_dir, use_master, mode):
+@pytest.mark.parametrize("mode", [0, 1], ids=["nccl", "p2p"])
+def test_world_one_bfloat16_pools(pkg, O, mode):
+    import torch
+    torch.cuda.set_device(0)
+    out = _run_rank(0, 1, pkg.zero1_unique_id(), pkg, O, torch, True, mode, bf=True)
+    _check(pkg, O, 1, [out], True, mode, bf=True)
+
+
+def _worker(rank, world, port, out_dir, use_master, mode, bf=False):
     import sys
     import torch
     import torch.distributed as dist
@@ -142,7 +160,7 @@ def _worker(rank, world, port, out_dir, use_master, mode):
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
     box = [pkg.zero1_unique_id() if rank == 0 else None]
     dist.broadcast_object_list(box, src=0)
-    out = _run_rank(rank, world, box[0], pkg, O, torch, use_master, mode)
+    out = _run_rank(rank, world, box[0], pkg, O, torch, use_master, mode, bf)
     np.savez(os.path.join(out_dir, f"rank{rank}.npz"), **out)
     dist.barrier()
     dist.destroy_process_group()
@@ -162,6 +180,21 @@ def test_sharded_step_on_several_gpus(pkg, O, tmp_path, world, mode):
         z = np.load(tmp_path / f"rank{r}.npz")
         outs.append({k: (z[k] if z[k].ndim else z[k].item()) for k in z.files})
     _check(pkg, O, world, outs, world == 2, mode)
+
+
+@pytest.mark.parametrize("mode", [0, 1], ids=["nccl", "p2p"])
+def test_bfloat16_pools_on_two_gpus(pkg, O, tmp_path, mode):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), False, mode, True), nprocs=2, join=True)
+    outs = []
+    for r in range(2):
+        z = np.load(tmp_path / f"rank{r}.npz")
+        outs.append({k: (z[k] if z[k].ndim else z[k].item()) for k in z.files})
+    _check(pkg, O, 2, outs, False, mode, bf=True)
 
 
 def _leaver(rank, world, port, out_dir):
