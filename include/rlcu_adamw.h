@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define RLCU_ABI_VERSION 1
+#define RLCU_ABI_VERSION 2
 
 /* status codes */
 enum {
@@ -46,6 +46,14 @@ enum {
  * RLCU_BF16 (bfloat16 parameters and gradients, same arithmetic in FP32, same options)
  * has no counterpart in RL.cu; its results are checked against the CPU restatement only. */
 enum { RLCU_F16 = 0, RLCU_F32 = 1, RLCU_BF16 = 2 };
+
+/* kind of a tensor's gradient (rlcu_tensor_desc.grad_dtype).  RL.cu keeps FP16 gradients for
+ * FP16 parameters, accumulated by cuBLAS with beta = 1 (src/kernels/linear.cu:85-98) and by
+ * FP16 atomics for the embedding (src/kernels/embedding.cu:62-67), which is where small
+ * gradients are lost before the optimizer sees them.  RLCU_GRAD_F32 lets a 16-bit parameter
+ * take its gradient from an FP32 buffer instead: 4 bytes read per element where the 16-bit
+ * gradient has 2, scaled in FP32 (never rounded through 16 bits).  No RL.cu counterpart. */
+enum { RLCU_GRAD_AS_PARAM = 0, RLCU_GRAD_F32 = 1 };
 
 /* per-tensor flags */
 enum {
@@ -65,7 +73,11 @@ enum {
                                        FP32 tensors are scaled in FP32.                   */
     RLCU_STEP_DEVICE_BIAS_CORRECTION = 2u, /* take 1-beta^t from the statistics record
                                        (written by the statistics pass when a device-side
-                                       scaler state is attached) instead of rlcu_hparams */
+                                       scaler state is attached) instead of rlcu_hparams.
+                                       The device value is the correctly rounded FP32 power;
+                                       it equals rlcu_bias_correction (the host's powf) except
+                                       at the rare steps where the C library's powf is one ulp
+                                       off (beta 0.999: t = 2958, 3606 with glibc 2.39)      */
     RLCU_STEP_ZERO_GRADS = 4u,      /* write zeros over each gradient after reading it:
                                        folds RL.cu's qwen3_gradients_zero (qwen3.cu:1109-1112)
                                        into the update                                   */
@@ -76,8 +88,11 @@ enum {
 
 /* flags of the statistics pass */
 enum {
-    RLCU_STAT_PARTIAL = 1u  /* only write sum_sq (this rank's share); the caller
-                               all-reduces it and calls rlcu_gradstat_finalize        */
+    RLCU_STAT_PARTIAL = 1u,   /* only write sum_sq (this rank's or this buffer's share); the
+                                 caller all-reduces it and calls rlcu_gradstat_finalize, or
+                                 follows with an RLCU_STAT_ACCUMULATE call                */
+    RLCU_STAT_ACCUMULATE = 2u /* rlcu_gradstat_flat_noalloc only: add this buffer's sum to
+                                 the sum_sq an earlier PARTIAL call left in the record     */
 };
 
 /* One parameter tensor.  Mirrors one slice of RL.cu's flat pools: param/grad
@@ -85,7 +100,8 @@ enum {
  * master from AdamWOptimizer's state (optimizer.h:150-156). 64 bytes. */
 typedef struct rlcu_tensor_desc {
     void*       param;        /* __half*, bfloat16* or float* by dtype; updated in place */
-    const void* grad;         /* same kind as param; may be NULL with GRAD_ZERO        */
+    const void* grad;         /* same kind as param, or float* with RLCU_GRAD_F32; may be
+                                 NULL with GRAD_ZERO                                   */
     float*      m;            /* first moment                                          */
     float*      v;            /* second moment                                         */
     float*      master;       /* FP32 master copy (F16/BF16 only) or NULL.  With a master,
@@ -95,7 +111,7 @@ typedef struct rlcu_tensor_desc {
                                  (optimizer.h:131-146)                                 */
     uint32_t    dtype;        /* RLCU_F16 / RLCU_F32 / RLCU_BF16                       */
     uint32_t    flags;        /* RLCU_TENSOR_*                                         */
-    uint32_t    reserved;     /* must be 0                                             */
+    uint32_t    grad_dtype;   /* RLCU_GRAD_AS_PARAM (0) or RLCU_GRAD_F32               */
 } rlcu_tensor_desc;
 
 /* Step hyper-parameters: AdamWOptimizer's public fields (optimizer.h:62-66) and
@@ -110,11 +126,16 @@ typedef struct rlcu_hparams {
  * by the update pass without a host round trip (RL.cu reads the sum back to the
  * host in the middle of the step, trainer.h:340). 64 bytes, 16-byte aligned. */
 typedef struct rlcu_stat {
-    double   sum_sq;       /* sum over all listed gradients of (g*unscale)^2            */
+    double   sum_sq;       /* sum over all listed gradients of (g*unscale)^2; NaN when some
+                              gradient was inf or NaN (that is how a partial sum carries
+                              the overflow through an all-reduce); +inf when finite FP32
+                              gradients have squares beyond FP32, which is not an overflow:
+                              norm is then +inf and a clip scales the gradients to zero   */
     float    norm;         /* sqrtf((float)sum_sq): the PRE-clip norm RL.cu logs        */
     float    coef;         /* what each gradient is multiplied by: unscale, times
                               max_norm/(norm+1e-6) when norm > max_norm (trainer.h:343-344) */
-    uint32_t found_inf;    /* 1: some gradient is inf/NaN -> the update writes nothing  */
+    uint32_t found_inf;    /* 1: some gradient is inf/NaN (tested on the stored value, not on
+                              its square) -> the update writes nothing                  */
     uint32_t clip_active;  /* 1: norm > max_norm                                        */
     float    bias_correction1; /* valid when a scaler state was attached                */
     float    bias_correction2;
@@ -183,9 +204,10 @@ int rlcu_half_to_float(float* dst, const void* src, int64_t n, void* stream);
  * (optimizer.h:188-250).  Tensors with n == 0 are allowed and ignored. */
 int rlcu_tensor_list_create(const rlcu_tensor_desc* descs, uint64_t count, rlcu_tensor_list** out);
 int rlcu_tensor_list_destroy(rlcu_tensor_list* list);
-/* Synchronises with the device and reports whether a bounded wait inside a kernel
- * launched on this list gave up since the last check (RLCU_ERR_TIMEOUT); only the
- * RLCU_STEP_BULK_COPY update has such waits.  Clears the condition. */
+/* Waits for every stream of the device (cudaDeviceSynchronize) and reports whether a
+ * bounded wait inside a kernel launched on this list gave up since the last check
+ * (RLCU_ERR_TIMEOUT); only the RLCU_STEP_BULK_COPY update has such waits.  Clears the
+ * condition. */
 int rlcu_tensor_list_check(rlcu_tensor_list* list);
 /* Runs a one-thread kernel whose bounded wait is certain to run out (it waits on a
  * barrier nothing completes) and reports it through the same path: the expected
@@ -224,6 +246,11 @@ int rlcu_gradstat(rlcu_tensor_list* list, float unscale, float max_norm,
  * and because some hot paths are not allowed to enter the allocator at all.
  *   n      : at most RLCU_NOALLOC_MAX_ELEMS; more is refused with RLCU_ERR_INVALID
  *   dtype  : RLCU_F16 or RLCU_F32
+ *   flags  : 0 for a single buffer.  The record covers exactly the one buffer of the call;
+ *            RL.cu's clip norm covers two pools (trainer.h:331-337), so for those call
+ *            once on half_pool with RLCU_STAT_PARTIAL (leaves only sum_sq in the record)
+ *            and then, on the same stream, on float_pool with RLCU_STAT_ACCUMULATE (adds
+ *            its sum to the record's and writes the finished record).
  * Calls on one device share the scratch: calls that overlap on the GPU race.
  * The first call on a device resolves the scratch address; make it at set-up,
  * before any stream capture.  Sums are taken per 8192-element chunk and added in
@@ -232,7 +259,7 @@ int rlcu_gradstat(rlcu_tensor_list* list, float unscale, float max_norm,
 #define RLCU_NOALLOC_MAX_ELEMS 2147483648ull
 int rlcu_gradstat_flat_noalloc(const void* grad, uint32_t dtype, uint64_t n,
                                float unscale, float max_norm,
-                               rlcu_stat* stat_out, void* stream);
+                               rlcu_stat* stat_out, uint32_t flags, void* stream);
 /* Completes a PARTIAL record after the caller has all-reduced stat->sum_sq. */
 int rlcu_gradstat_finalize(rlcu_stat* stat, float unscale, float max_norm,
                            rlcu_scaler_state* scaler, void* stream);

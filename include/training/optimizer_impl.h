@@ -82,7 +82,12 @@ public:
     }
 
     void set_lr(float new_lr) { lr = new_lr; }
-    int get_step() const { return step_; }
+    // Adam step counter t.  A step that clip_and_step found non-finite gradients in wrote
+    // nothing and does not count; the counter is settled when that step's record is read.
+    int get_step() const {
+        settle();
+        return step_;
+    }
 
     float* fp16_master() { return master_; }
     float* fp16_m() { return m16_; }
@@ -103,6 +108,7 @@ public:
 
     // AdamWOptimizer::step of RL.cu (optimizer.h:119-147): no clipping here.
     void step(Grads* grads, cudaStream_t stream = 0) {
+        settle();
         bind(grads);
         step_++;
         const rlcu_hparams hp = hparams();
@@ -114,6 +120,7 @@ public:
     // with the same FP16 re-rounding.  max_norm <= 0 disables the clip
     // (trainer.h:280).  Nothing here waits for the GPU.
     void clip_and_step_async(Grads* grads, float max_norm, cudaStream_t stream = 0) {
+        settle();
         bind(grads);
         step_++;
         const rlcu_hparams hp = hparams();
@@ -123,13 +130,19 @@ public:
         check_cuda(cudaMemcpyAsync(h_stat_, d_stat_, sizeof(rlcu_stat), cudaMemcpyDeviceToHost, stream),
                    "statistics read-back");
         check_cuda(cudaEventRecord(stat_ready_, stream), "cudaEventRecord");
+        pending_ = true;
     }
 
     // The pre-clip gradient norm of the last clip_and_step_async (what RL.cu logs
     // as grad_norm, trainer.h:322, 351).  Waits only for that step's record.
     float last_grad_norm() {
-        check_cuda(cudaEventSynchronize(stat_ready_), "cudaEventSynchronize");
+        settle();
         return h_stat_->norm;
+    }
+    // Whether the last clip_and_step found an inf/NaN gradient and therefore wrote nothing.
+    bool last_step_skipped() {
+        settle();
+        return h_stat_->found_inf != 0;
     }
 
     // Same, returning the norm at once like Trainer::clip_grad_norm_ does.
@@ -142,7 +155,7 @@ public:
 
 private:
     Model* model_ = nullptr;
-    int step_ = 0;
+    mutable int step_ = 0;
     int layers_ = 0;
     float* state16_ = nullptr;   // one allocation: [master | m | v], as optimizer.h:224-236
     float* state32_ = nullptr;   // one allocation: [m | v]
@@ -153,9 +166,21 @@ private:
     const void* bound_half_ = nullptr;
     const void* bound_float_ = nullptr;
     bool bound_freeze_ = false, bound_workspace_ = false;
+    float bound_wd_ = 0.0f;
+    mutable bool pending_ = false;             // a clip_and_step record has not been looked at yet
     rlcu_stat* d_stat_ = nullptr;
     rlcu_stat* h_stat_ = nullptr;      // pinned
     cudaEvent_t stat_ready_ = nullptr;
+
+    // Waits for the record of the last clip_and_step (already there in a training loop, which
+    // logs the norm of every step) and takes a skipped step back out of the counter, so that
+    // bias correction follows the steps that were applied.
+    void settle() const {
+        if (!pending_) return;
+        check_cuda(cudaEventSynchronize(stat_ready_), "cudaEventSynchronize");
+        pending_ = false;
+        if (h_stat_->found_inf) step_--;
+    }
 
     rlcu_hparams hparams() const {
         rlcu_hparams hp;
@@ -216,7 +241,8 @@ private:
         memset(h_stat_, 0, sizeof(rlcu_stat));
         check_cuda(cudaEventCreateWithFlags(&stat_ready_, cudaEventDisableTiming), "cudaEventCreate");
         check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
-        printf("[AdamW] fp16=%zu params (%.1f MB state)  fp32=%zu params (%.2f MB state)  (lr=%.1e wd=%.2f)\n",
+        printf("[AdamW] optimizer state ready: %zu FP16 parameters with FP32 master/m/v (%.1f MB), "
+               "%zu FP32 parameters with m/v (%.2f MB); lr %.1e, weight decay %.2f\n",
                n16_, n16_ * 12 / (1024.0 * 1024.0), n32_, n32_ * 8 / (1024.0 * 1024.0), lr, weight_decay);
     }
 
@@ -224,7 +250,8 @@ private:
     // RL.cu allocates its gradient pools once, so this runs on the first step only.
     void bind(Grads* grads) {
         if (list_ && bound_half_ == grads->half_pool && bound_float_ == grads->float_pool &&
-            bound_freeze_ == freeze_embed && bound_workspace_ == norm_includes_workspace)
+            bound_freeze_ == freeze_embed && bound_workspace_ == norm_includes_workspace &&
+            bound_wd_ == weight_decay)
             return;
         if (list_) check(rlcu_tensor_list_destroy(list_), "rlcu_tensor_list_destroy");
         list_ = nullptr;
@@ -250,8 +277,10 @@ private:
             d[3].flags = RLCU_TENSOR_NORM_ONLY;
             count = 4;
         }
-        // the weight-decay value is baked into the list: rebuild if it is changed later
+        // the weight-decay value is baked into the list, so a change of the public field
+        // rebuilds it (RL.cu passes weight_decay to the launcher on every step, optimizer.h:126-129)
         check(rlcu_tensor_list_create(d, count, &list_), "rlcu_tensor_list_create");
+        bound_wd_ = weight_decay;
         bound_half_ = grads->half_pool;
         bound_float_ = grads->float_pool;
         bound_freeze_ = freeze_embed;

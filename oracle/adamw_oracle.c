@@ -177,9 +177,10 @@ double orc_sum_sq_half(const uint16_t* g, int64_t n, float unscale, int threads)
     int nt = pick_threads(threads);
     #pragma omp parallel for num_threads(nt) schedule(static) reduction(+:s)
     for (int64_t i = 0; i < n; i++) {
-        float x = orc_h2f(g[i]) * unscale;         /* trainer.h:108-109, FP32 product */
+        float raw = orc_h2f(g[i]);
+        float x = raw * unscale;                   /* trainer.h:108-109, FP32 product */
         float sq = x * x;
-        if (isfinite(sq)) s += (double)sq;
+        if (isfinite(raw)) s += (double)sq;        /* inf/NaN elements are reported through found_inf */
     }
     return s;
 }
@@ -189,9 +190,10 @@ double orc_sum_sq_bf16(const uint16_t* g, int64_t n, float unscale, int threads)
     int nt = pick_threads(threads);
     #pragma omp parallel for num_threads(nt) schedule(static) reduction(+:s)
     for (int64_t i = 0; i < n; i++) {
-        float x = orc_bf2f(g[i]) * unscale;
+        float raw = orc_bf2f(g[i]);
+        float x = raw * unscale;
         float sq = x * x;
-        if (isfinite(sq)) s += (double)sq;
+        if (isfinite(raw)) s += (double)sq;
     }
     return s;
 }
@@ -202,8 +204,8 @@ double orc_sum_sq_float(const float* g, int64_t n, float unscale, int threads) {
     #pragma omp parallel for num_threads(nt) schedule(static) reduction(+:s)
     for (int64_t i = 0; i < n; i++) {
         float x = g[i] * unscale;                  /* trainer.h:125-126 */
-        float sq = x * x;
-        if (isfinite(sq)) s += (double)sq;
+        float sq = x * x;                          /* FP32: a finite element's square may be +inf, */
+        if (isfinite(g[i])) s += (double)sq;       /* as in the reference's FP32 accumulation       */
     }
     return s;
 }
@@ -272,7 +274,11 @@ void orc_gradstat(const orc_tensor* t, uint64_t count, float unscale, float max_
     uint32_t inf = extra_found_inf;
     for (uint64_t k = 0; k < count; k++) {
         if (t[k].n == 0 || (t[k].flags & ORC_FLAG_GRAD_ZERO)) continue;
-        if (t[k].dtype == ORC_F16) {
+        if (t[k].grad_dtype == ORC_GRAD_F32 && t[k].dtype != ORC_F32) {
+            /* 16-bit parameter with an FP32 gradient: the FP32 rules (trainer.h:120-133) */
+            s += orc_sum_sq_float((const float*)t[k].grad, (int64_t)t[k].n, unscale, threads);
+            inf |= orc_count_nonfinite_float((const float*)t[k].grad, (int64_t)t[k].n) != 0;
+        } else if (t[k].dtype == ORC_F16) {
             s += orc_sum_sq_half((const uint16_t*)t[k].grad, (int64_t)t[k].n, unscale, threads);
             inf |= orc_count_nonfinite_half((const uint16_t*)t[k].grad, (int64_t)t[k].n) != 0;
         } else if (t[k].dtype == ORC_BF16) {
@@ -306,12 +312,19 @@ int orc_multi_step(const orc_tensor* t, uint64_t count, const orc_hparams* hp,
         int64_t n = (int64_t)d->n;
         if (d->dtype == ORC_F16 || d->dtype == ORC_BF16) {
             const int bf = d->dtype == ORC_BF16;
+            const int gf32 = d->grad_dtype == ORC_GRAD_F32;
             uint16_t* p = (uint16_t*)d->param;
             const uint16_t* g = (const uint16_t*)d->grad;
+            const float* gf = (const float*)d->grad;
             #pragma omp parallel for num_threads(nt) schedule(static)
             for (int64_t i = 0; i < n; i++) {
-                float x = zero ? 0.0f : (bf ? orc_bf2f(g[i]) : orc_h2f(g[i])) * coef;
-                if (round_clip) x = bf ? orc_bf2f(orc_f2bf(x)) : orc_h2f(orc_f2h(x));   /* trainer.h:138 */
+                float x;
+                if (gf32) {
+                    x = zero ? 0.0f : gf[i] * coef;                                   /* trainer.h:144 */
+                } else {
+                    x = zero ? 0.0f : (bf ? orc_bf2f(g[i]) : orc_h2f(g[i])) * coef;
+                    if (round_clip) x = bf ? orc_bf2f(orc_f2bf(x)) : orc_h2f(orc_f2h(x));   /* trainer.h:138 */
+                }
                 float w0 = d->master ? d->master[i] : (bf ? orc_bf2f(p[i]) : orc_h2f(p[i]));
                 float w = upd(w0, x, &d->m[i], &d->v[i], &kk, rounding);
                 if (d->master) d->master[i] = w;

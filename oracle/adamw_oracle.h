@@ -54,11 +54,14 @@ enum { ORC_UNFUSED = 0, ORC_NVCC = ORC_ROUNDING(2, 2, 0, 0) };
 /* element kinds and flags; binary-compatible with rlcu_tensor_desc */
 enum { ORC_F16 = 0, ORC_F32 = 1, ORC_BF16 = 2 };   /* BF16: no reference counterpart, parity unpinned */
 enum { ORC_FLAG_NORM_ONLY = 1u, ORC_FLAG_GRAD_ZERO = 2u };
+/* gradient kind: as the parameter, or FP32 for a 16-bit parameter (no reference counterpart:
+ * the reference accumulates FP16 gradients, src/kernels/linear.cu:85-98; parity unpinned) */
+enum { ORC_GRAD_AS_PARAM = 0u, ORC_GRAD_F32 = 1u };
 enum { ORC_STEP_ROUND_CLIP_FP16 = 1u };
 
 typedef struct orc_tensor {
     void*       param;    /* uint16_t* (IEEE binary16 bits) or float*          */
-    const void* grad;     /* same element kind as param                        */
+    const void* grad;     /* same element kind as param, or float* (ORC_GRAD_F32) */
     float*      m;
     float*      v;
     float*      master;   /* FP32 master copy or NULL (F16 only)               */
@@ -66,7 +69,7 @@ typedef struct orc_tensor {
     float       weight_decay;
     uint32_t    dtype;
     uint32_t    flags;
-    uint32_t    reserved;
+    uint32_t    grad_dtype;
 } orc_tensor;
 
 typedef struct orc_hparams {
@@ -122,7 +125,11 @@ void orc_adamw_fp32(float* w, const float* grad, float* m, float* v, int64_t n,
                     int rounding, int threads);
 
 /* include/training/trainer.h:103-133; accumulation in FP64 (the reference's
- * FP32 atomic order is unspecified, so the oracle gives the exact sum). */
+ * FP32 atomic order is unspecified, so the oracle gives the exact sum) of squares
+ * taken in FP32 as the reference takes them.  Elements that are inf or NaN are left
+ * out of the sum and reported by orc_count_nonfinite_*; a finite FP32 element whose
+ * square overflows FP32 makes the sum +inf (norm +inf, a clip then scales to zero),
+ * which is what the reference's kernels do with it, and is NOT an overflowed step. */
 double orc_sum_sq_half(const uint16_t* g, int64_t n, float unscale, int threads);
 double orc_sum_sq_float(const float* g, int64_t n, float unscale, int threads);
 double orc_sum_sq_bf16(const uint16_t* g, int64_t n, float unscale, int threads);

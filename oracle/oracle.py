@@ -30,6 +30,7 @@ def rounding(m_mode, v_mode, w_fused, d_fused):
 NVCC = rounding(2, 2, 0, 0)
 F16, F32, BF16 = 0, 1, 2
 FLAG_NORM_ONLY, FLAG_GRAD_ZERO = 1, 2
+GRAD_AS_PARAM, GRAD_F32 = 0, 1
 STEP_ROUND_CLIP_FP16 = 1
 
 
@@ -37,7 +38,7 @@ class Tensor(C.Structure):
     """Binary layout of ``orc_tensor`` (and of the product's ``rlcu_tensor_desc``)."""
     _fields_ = [("param", C.c_void_p), ("grad", C.c_void_p), ("m", C.c_void_p), ("v", C.c_void_p),
                 ("master", C.c_void_p), ("n", C.c_uint64), ("weight_decay", C.c_float),
-                ("dtype", C.c_uint32), ("flags", C.c_uint32), ("reserved", C.c_uint32)]
+                ("dtype", C.c_uint32), ("flags", C.c_uint32), ("grad_dtype", C.c_uint32)]
 
 
 class HParams(C.Structure):
@@ -179,6 +180,7 @@ def make_tensors(entries) -> C.Array:
         t.weight_decay = e.get("wd", 0.0)
         t.dtype = e.get("dtype", F16 if (p if p is not None else e["g"]).dtype == np.uint16 else F32)
         t.flags = e.get("flags", 0)
+        t.grad_dtype = e.get("grad_dtype", GRAD_AS_PARAM)
     return arr
 
 

@@ -22,9 +22,10 @@ LIB_PATH = os.path.join(_HERE, "lib", "librlcu_b200.so")
 
 OK, ERR_INVALID, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_UNSUPPORTED = range(6)
 F16, F32, BF16 = 0, 1, 2
+GRAD_AS_PARAM, GRAD_F32 = 0, 1
 TENSOR_NORM_ONLY, TENSOR_GRAD_ZERO = 1, 2
 STEP_ROUND_CLIP_FP16, STEP_DEVICE_BIAS_CORRECTION, STEP_ZERO_GRADS, STEP_BULK_COPY = 1, 2, 4, 8
-STAT_PARTIAL = 1
+STAT_PARTIAL, STAT_ACCUMULATE = 1, 2
 
 # every symbol include/rlcu_adamw.h declares
 EXPORTS = [
@@ -59,7 +60,7 @@ class TensorDesc(C.Structure):
     """``rlcu_tensor_desc`` (64 bytes)."""
     _fields_ = [("param", C.c_void_p), ("grad", C.c_void_p), ("m", C.c_void_p), ("v", C.c_void_p),
                 ("master", C.c_void_p), ("n", C.c_uint64), ("weight_decay", C.c_float),
-                ("dtype", C.c_uint32), ("flags", C.c_uint32), ("reserved", C.c_uint32)]
+                ("dtype", C.c_uint32), ("flags", C.c_uint32), ("grad_dtype", C.c_uint32)]
 
 
 class HParams(C.Structure):
@@ -148,7 +149,7 @@ def lib() -> C.CDLL:
     L.rlcu_gradstat.argtypes = [vp, f, f, vp, vp, u32, vp]
     L.rlcu_gradstat_finalize.argtypes = [vp, f, f, vp, vp]
     L.rlcu_adamw_multi_step.argtypes = [vp, vp, vp, u32, vp]
-    L.rlcu_gradstat_flat_noalloc.argtypes = [vp, u32, u64, f, f, vp, vp]
+    L.rlcu_gradstat_flat_noalloc.argtypes = [vp, u32, u64, f, f, vp, u32, vp]
     L.rlcu_zero1_make_plan.argtypes = [vp, u64, C.c_int, C.c_int, vp]
     L.rlcu_zero1_plan_pieces.argtypes = [vp, u64, C.c_int, C.c_int, vp, vp, vp, vp, vp]
     L.rlcu_zero1_unique_id.argtypes = [vp]
@@ -254,11 +255,12 @@ def gradstat_finalize(stat_ptr, unscale=1.0, max_norm=0.0, scaler_ptr=None, stre
     check(lib().rlcu_gradstat_finalize(stat_ptr, unscale, max_norm, scaler_ptr, stream))
 
 
-def gradstat_flat_noalloc(grad_ptr, dtype, n, stat_ptr, unscale=1.0, max_norm=0.0, stream=None):
+def gradstat_flat_noalloc(grad_ptr, dtype, n, stat_ptr, unscale=1.0, max_norm=0.0, flags=0, stream=None):
     """Statistics of one flat gradient buffer without any device allocation (see the header:
     fixed scratch inside the library, at most ``NOALLOC_MAX_ELEMS`` elements, calls must not
-    overlap on the GPU)."""
-    check(lib().rlcu_gradstat_flat_noalloc(grad_ptr, dtype, n, unscale, max_norm, stat_ptr, stream))
+    overlap on the GPU).  Two buffers of one step: ``STAT_PARTIAL`` on the first call,
+    ``STAT_ACCUMULATE`` on the second."""
+    check(lib().rlcu_gradstat_flat_noalloc(grad_ptr, dtype, n, unscale, max_norm, stat_ptr, flags, stream))
 
 
 # ---------------------------------------------------------------------------

@@ -78,7 +78,7 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 __device__ __forceinline__ bool bulk_eligible(const WorkItem& it) {
     const uint32_t kind = it.flags & kItemKindMask;
     return it.count == (uint32_t)kChunk && (it.flags & kItemVec16) && kind != kItemKindF32 &&
-           !(it.flags & (RLCU_TENSOR_NORM_ONLY | kItemBF16));
+           !(it.flags & (RLCU_TENSOR_NORM_ONLY | kItemBF16 | kItemGradF32));
 }
 
 // Issues the loads of one tile into a stage (one thread).

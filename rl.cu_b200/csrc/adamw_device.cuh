@@ -36,6 +36,7 @@ constexpr uint32_t kItemKindF32 = 2u << 8;
 constexpr uint32_t kItemVec16 = 1u << 10;       // every pointer 16-byte aligned
 constexpr uint32_t kItemVec32 = 1u << 11;       // FP32 pointers 32-byte aligned too
 constexpr uint32_t kItemBF16 = 1u << 12;        // the 16-bit data of an F16-kind item is bfloat16
+constexpr uint32_t kItemGradF32 = 1u << 13;     // an F16-kind item whose gradient is FP32
 
 // One unit of work: at most kChunk consecutive elements of one tensor, with
 // every pointer already advanced to the first of them.  64 bytes so that a
@@ -214,6 +215,44 @@ __device__ __forceinline__ float round_through_half(float x) {
 __device__ __forceinline__ float round_through_16(float x, bool bf) {
     return bf ? __bfloat162float(__float2bfloat16_rn(x)) : round_through_half(x);
 }
+
+// ---- non-finite detection ---------------------------------------------------
+// x*0 is NaN exactly when x is inf or NaN, and NaN is sticky under addition, so one
+// multiply-add per value (per pair, for packed 16-bit data) into an accumulator that
+// starts at zero records whether any value seen was non-finite.  The test is on the
+// stored gradient itself, not on its square: a finite FP32 gradient whose square
+// overflows FP32 is not an overflowed step.
+struct NanProbe {
+    float f = 0.0f;        // FP32 values
+    uint32_t h = 0u;       // a half2 (+0, +0)
+    uint32_t b = 0u;       // a bfloat162 (+0, +0)
+
+    __device__ __forceinline__ void add(float x) { f = __fmaf_rn(x, 0.0f, f); }
+    __device__ __forceinline__ void add_pair16(uint32_t w, bool bf) {
+        if (bf) {
+            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&w);
+            __nv_bfloat162 acc = *reinterpret_cast<const __nv_bfloat162*>(&b);
+            acc = __hfma2(a, __float2bfloat162_rn(0.0f), acc);
+            b = *reinterpret_cast<const uint32_t*>(&acc);
+        } else {
+            const __half2 a = *reinterpret_cast<const __half2*>(&w);
+            __half2 acc = *reinterpret_cast<const __half2*>(&h);
+            acc = __hfma2(a, __float2half2_rn(0.0f), acc);
+            h = *reinterpret_cast<const uint32_t*>(&acc);
+        }
+    }
+    __device__ __forceinline__ void add_h8(uint4 x, bool bf) {
+        add_pair16(x.x, bf);
+        add_pair16(x.y, bf);
+        add_pair16(x.z, bf);
+        add_pair16(x.w, bf);
+    }
+    __device__ __forceinline__ bool bad() const {
+        const float2 hf = __half22float2(*reinterpret_cast<const __half2*>(&h));
+        const float b0 = __uint_as_float(b << 16), b1 = __uint_as_float(b & 0xFFFF0000u);
+        return isnan(f) || isnan(hf.x) || isnan(hf.y) || isnan(b0) || isnan(b1);
+    }
+};
 
 // ---- reduction --------------------------------------------------------------
 // Fixed-order sum over the CTA: xor-shuffle tree inside each warp, then the

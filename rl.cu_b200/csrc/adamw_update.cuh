@@ -51,20 +51,32 @@ __device__ __forceinline__ float xform_h(float g, float coef, bool bf) {
     return x;
 }
 
+__device__ __forceinline__ F8 f8_zero() {
+    F8 z;
+#pragma unroll
+    for (int i = 0; i < 8; i++) z.a[i] = 0.0f;
+    return z;
+}
+
 // One group of 8 FP16 elements with every access vectorised.
 //   KIND 0: weight read from the FP16 parameter; KIND 1: from the FP32 master.
-template <int KIND, bool V32, bool ROUND, int U, bool PEERS>
+//   GF32: the gradient is FP32 (16-bit parameter whose gradient was accumulated in FP32);
+//         it is scaled in FP32 like RL.cu's scale_float_kernel (trainer.h:142-145), never
+//         rounded through 16 bits.
+template <int KIND, bool V32, bool ROUND, int U, bool PEERS, bool GF32 = false>
 __device__ __forceinline__ void f16_groups(const WorkItem& it, int first_group, int group_stride,
                                            const StepConsts& c, float decay, const GradXform& xf,
                                            const PeerOut& peers) {
+    static_assert(!(GF32 && ROUND), "FP32 gradients are not rounded through 16 bits");
     uint4 gw[U], pw[U];
-    F8 m[U], v[U], w[U];
+    F8 gf[U], m[U], v[U], w[U];
     const bool zero = (it.flags & RLCU_TENSOR_GRAD_ZERO) != 0;
     const bool bf = (it.flags & kItemBF16) != 0;
 #pragma unroll
     for (int u = 0; u < U; u++) {
         const size_t e = (size_t)(first_group + u * group_stride) * kGroup;
-        gw[u] = zero ? make_uint4(0, 0, 0, 0) : ld_h8(static_cast<const __half*>(it.g) + e);
+        if constexpr (GF32) gf[u] = zero ? f8_zero() : ld_f8<V32>(static_cast<const float*>(it.g) + e);
+        else gw[u] = zero ? make_uint4(0, 0, 0, 0) : ld_h8(static_cast<const __half*>(it.g) + e);
         if constexpr (KIND == 0) pw[u] = ld_h8(static_cast<const __half*>(it.p) + e);
         else w[u] = ld_f8<V32>(it.master + e);
         m[u] = ld_f8<V32>(it.m + e);
@@ -73,19 +85,25 @@ __device__ __forceinline__ void f16_groups(const WorkItem& it, int first_group, 
 #pragma unroll
     for (int u = 0; u < U; u++) {
         const size_t e = (size_t)(first_group + u * group_stride) * kGroup;
-        F8 g = x8_to_f8(gw[u], bf);
+        F8 g;
+        if constexpr (GF32) g = gf[u];
+        else g = x8_to_f8(gw[u], bf);
         if constexpr (KIND == 0) w[u] = x8_to_f8(pw[u], bf);
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            const float x = xform_h<ROUND>(g.a[i], xf.coef, bf);
+            float x;
+            if constexpr (GF32) x = __fmul_rn(g.a[i], xf.coef);          // trainer.h:144
+            else x = xform_h<ROUND>(g.a[i], xf.coef, bf);
             w[u].a[i] = adamw_element(w[u].a[i], x, m[u].a[i], v[u].a[i], c, decay);
         }
         st_f8<V32>(it.m + e, m[u]);
         st_f8<V32>(it.v + e, v[u]);
         if constexpr (KIND == 1) st_f8<V32>(it.master + e, w[u]);
         store_param_h8<PEERS>(static_cast<__half*>(it.p) + e, f8_to_x8(w[u], bf), peers);
-        if (xf.zero_grads && !zero)
-            st_h8(const_cast<__half*>(static_cast<const __half*>(it.g)) + e, make_uint4(0, 0, 0, 0));
+        if (xf.zero_grads && !zero) {
+            if constexpr (GF32) st_f8<V32>(const_cast<float*>(static_cast<const float*>(it.g)) + e, f8_zero());
+            else st_h8(const_cast<__half*>(static_cast<const __half*>(it.g)) + e, make_uint4(0, 0, 0, 0));
+        }
     }
 }
 
@@ -145,22 +163,29 @@ __device__ __forceinline__ void scalar_range(const WorkItem& it, uint32_t begin,
             if (xf.zero_grads && !zero) g[i] = 0.0f;
         } else {
             __half* p = static_cast<__half*>(it.p);
-            __half* g = const_cast<__half*>(static_cast<const __half*>(it.g));
             const bool bf = (it.flags & kItemBF16) != 0;
-            float x = zero ? 0.0f : __fmul_rn(x_to_f(__half_as_ushort(g[i]), bf), xf.coef);
-            if (xf.round_half) x = round_through_16(x, bf);
+            float x;
+            if (it.flags & kItemGradF32) {
+                float* g = const_cast<float*>(static_cast<const float*>(it.g));
+                x = zero ? 0.0f : __fmul_rn(g[i], xf.coef);
+                if (xf.zero_grads && !zero) g[i] = 0.0f;
+            } else {
+                __half* g = const_cast<__half*>(static_cast<const __half*>(it.g));
+                x = zero ? 0.0f : __fmul_rn(x_to_f(__half_as_ushort(g[i]), bf), xf.coef);
+                if (xf.round_half) x = round_through_16(x, bf);
+                if (xf.zero_grads && !zero) g[i] = __float2half_rn(0.0f);
+            }
             const float w0 = (kind == kItemKindF16Master) ? it.master[i] : x_to_f(__half_as_ushort(p[i]), bf);
             const float w = adamw_element(w0, x, m, v, c, decay);
             if (kind == kItemKindF16Master) it.master[i] = w;
             store_param_h<PEERS>(p + i, __ushort_as_half(f_to_x(w, bf)), peers);
-            if (xf.zero_grads && !zero) g[i] = __float2half_rn(0.0f);
         }
         it.m[i] = m;
         it.v[i] = v;
     }
 }
 
-template <int KIND, bool V32, bool ROUND, bool PEERS>
+template <int KIND, bool V32, bool ROUND, bool PEERS, bool GF32 = false>
 __device__ __forceinline__ void vector_item(const WorkItem& it, const StepConsts& c, float decay,
                                             const GradXform& xf, const PeerOut& peers) {
     const int groups = it.count / kGroup;
@@ -171,18 +196,20 @@ __device__ __forceinline__ void vector_item(const WorkItem& it, const StepConsts
         for (int b = 0; b < kGroupsPerThread / U; b++) {
             const int first = threadIdx.x + b * U * kThreads;
             if constexpr (KIND == 2) f32_groups<V32, U>(it, first, kThreads, c, decay, xf);
-            else f16_groups<KIND, V32, ROUND, U, PEERS>(it, first, kThreads, c, decay, xf, peers);
+            else f16_groups<KIND, V32, ROUND, U, PEERS, GF32>(it, first, kThreads, c, decay, xf, peers);
         }
     } else {
         for (int grp = threadIdx.x; grp < groups; grp += kThreads) {
             if constexpr (KIND == 2) f32_groups<V32, 1>(it, grp, 0, c, decay, xf);
-            else f16_groups<KIND, V32, ROUND, 1, PEERS>(it, grp, 0, c, decay, xf, peers);
+            else f16_groups<KIND, V32, ROUND, 1, PEERS, GF32>(it, grp, 0, c, decay, xf, peers);
         }
         scalar_range<PEERS>(it, groups * kGroup, it.count, c, decay, xf, peers);
     }
 }
 
-template <bool PEERS>
+// GF32 says whether the table may hold 16-bit parameters with FP32 gradients; kernels are
+// instantiated both ways so that lists without such tensors run the code they always ran.
+template <bool PEERS, bool GF32 = false>
 __device__ __forceinline__ void process_item(const WorkItem& it, const StepConsts& c,
                                              const GradXform& xf, const PeerOut& peers) {
     if (it.flags & RLCU_TENSOR_NORM_ONLY) return;
@@ -193,6 +220,18 @@ __device__ __forceinline__ void process_item(const WorkItem& it, const StepConst
         return;
     }
     const bool v32 = (it.flags & kItemVec32) != 0;
+    if constexpr (GF32) {
+        if (it.flags & kItemGradF32) {
+            if (kind == kItemKindF16) {
+                if (v32) vector_item<0, true, false, PEERS, true>(it, c, decay, xf, peers);
+                else vector_item<0, false, false, PEERS, true>(it, c, decay, xf, peers);
+            } else {
+                if (v32) vector_item<1, true, false, PEERS, true>(it, c, decay, xf, peers);
+                else vector_item<1, false, false, PEERS, true>(it, c, decay, xf, peers);
+            }
+            return;
+        }
+    }
     if (kind == kItemKindF16) {
         if (xf.round_half) {
             if (v32) vector_item<0, true, true, PEERS>(it, c, decay, xf, peers);
@@ -232,12 +271,21 @@ __device__ __forceinline__ void clear_gradients(const WorkItem* table, uint32_t 
     for (uint32_t idx = blockIdx.x; idx < n_items; idx += gridDim.x) {
         const WorkItem it = load_item(table, idx);
         if (it.flags & (RLCU_TENSOR_NORM_ONLY | RLCU_TENSOR_GRAD_ZERO)) continue;
-        if ((it.flags & kItemKindMask) == kItemKindF32) {
+        const bool f32 = (it.flags & kItemKindMask) == kItemKindF32 || (it.flags & kItemGradF32);
+        const uint32_t per_vec = f32 ? 4u : 8u;          // elements in 16 bytes
+        uint32_t done = 0;
+        if (it.flags & kItemVec16) {                     // the gradient pointer is 16-byte aligned
+            uint4* g = reinterpret_cast<uint4*>(const_cast<void*>(it.g));
+            const uint32_t vecs = it.count / per_vec;
+            for (uint32_t i = threadIdx.x; i < vecs; i += blockDim.x) __stcs(g + i, make_uint4(0, 0, 0, 0));
+            done = vecs * per_vec;
+        }
+        if (f32) {
             float* g = const_cast<float*>(static_cast<const float*>(it.g));
-            for (uint32_t i = threadIdx.x; i < it.count; i += blockDim.x) g[i] = 0.0f;
+            for (uint32_t i = done + threadIdx.x; i < it.count; i += blockDim.x) g[i] = 0.0f;
         } else {
             __half* g = const_cast<__half*>(static_cast<const __half*>(it.g));
-            for (uint32_t i = threadIdx.x; i < it.count; i += blockDim.x) g[i] = __float2half_rn(0.0f);
+            for (uint32_t i = done + threadIdx.x; i < it.count; i += blockDim.x) g[i] = __float2half_rn(0.0f);
         }
     }
 }

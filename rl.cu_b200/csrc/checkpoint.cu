@@ -3,8 +3,11 @@
 // is this library's own.  Host I/O plus staged device copies; no kernels.
 #include "rlcu_adamw.h"
 
+#include <unistd.h>
+
 #include <cstdio>
 #include <cstring>
+#include <string>
 #include <vector>
 
 #include "host_util.h"
@@ -56,16 +59,25 @@ int rlcu_checkpoint_save(const char* path, const rlcu_checkpoint_info* info,
     if (info->state_elems && (!m || !v)) return set_error(RLCU_ERR_INVALID, "null state arrays");
     if ((info->has_master != 0) != (master != nullptr) && info->state_elems)
         return set_error(RLCU_ERR_INVALID, "has_master does not match the master pointer");
+    // Written beside the target and renamed over it once complete and on disk, so a crash
+    // or a full disk in mid-save leaves the previous checkpoint as it was.
+    const std::string tmp = std::string(path) + ".tmp";
+    struct Cleanup {                        // removes the partial file on every early return
+        const std::string& name;
+        bool armed = false;
+        ~Cleanup() { if (armed) remove(name.c_str()); }
+    } cleanup{tmp};
     File out;
-    out.f = fopen(path, "wb");
-    if (!out.f) return set_error(RLCU_ERR_INVALID, "cannot open %s for writing", path);
+    out.f = fopen(tmp.c_str(), "wb");
+    if (!out.f) return set_error(RLCU_ERR_INVALID, "cannot open %s for writing", tmp.c_str());
+    cleanup.armed = true;
     Header h;
     memset(&h, 0, sizeof(h));
     memcpy(h.magic, kMagic, 8);
     h.version = 1;
     h.header_bytes = sizeof(Header);
     h.info = *info;
-    if (fwrite(&h, sizeof(h), 1, out.f) != 1) return set_error(RLCU_ERR_INVALID, "write to %s failed", path);
+    if (fwrite(&h, sizeof(h), 1, out.f) != 1) return set_error(RLCU_ERR_INVALID, "write to %s failed", tmp.c_str());
 
     cudaStream_t s = (cudaStream_t)stream;
     std::vector<unsigned char> stage(kStage);
@@ -79,11 +91,16 @@ int rlcu_checkpoint_save(const char* path, const rlcu_checkpoint_info* info,
                                       cudaMemcpyDeviceToHost, s));
             RLCU_CUDA(cudaStreamSynchronize(s));
             sum = fnv1a(sum, stage.data(), n);
-            if (fwrite(stage.data(), 1, n, out.f) != n) return set_error(RLCU_ERR_INVALID, "write to %s failed", path);
+            if (fwrite(stage.data(), 1, n, out.f) != n) return set_error(RLCU_ERR_INVALID, "write to %s failed", tmp.c_str());
         }
     }
-    if (fwrite(&sum, sizeof(sum), 1, out.f) != 1 || fflush(out.f) != 0)
-        return set_error(RLCU_ERR_INVALID, "write to %s failed", path);
+    if (fwrite(&sum, sizeof(sum), 1, out.f) != 1 || fflush(out.f) != 0 || fsync(fileno(out.f)) != 0)
+        return set_error(RLCU_ERR_INVALID, "write to %s failed", tmp.c_str());
+    FILE* f = out.f;
+    out.f = nullptr;
+    if (fclose(f) != 0) return set_error(RLCU_ERR_INVALID, "closing %s failed", tmp.c_str());
+    if (rename(tmp.c_str(), path) != 0) return set_error(RLCU_ERR_INVALID, "cannot rename %s to %s", tmp.c_str(), path);
+    cleanup.armed = false;
     return RLCU_OK;
 }
 
@@ -117,24 +134,39 @@ int rlcu_checkpoint_load(const char* path, rlcu_checkpoint_info* info_out,
                          info.has_master ? "has" : "lacks", master ? "passed" : "did not pass");
     if (info.state_elems && (!m || !v)) return set_error(RLCU_ERR_INVALID, "null state arrays");
 
-    cudaStream_t s = (cudaStream_t)stream;
+    // First pass, host only: length and checksum.  Nothing is copied into the caller's
+    // live state until the whole file is known to be good.
     std::vector<unsigned char> stage(kStage);
+    const int n_arrays = info.has_master ? 3 : 2;
+    const size_t bytes = (size_t)info.state_elems * sizeof(float);
     uint64_t sum = 14695981039346656037ull;
-    float* arrays[3] = {m, v, master};
-    for (int a = 0; a < (info.has_master ? 3 : 2); a++) {
-        const size_t bytes = (size_t)info.state_elems * sizeof(float);
+    for (int a = 0; a < n_arrays; a++) {
         for (size_t off = 0; off < bytes; off += kStage) {
             const size_t n = bytes - off < kStage ? bytes - off : kStage;
             if (fread(stage.data(), 1, n, in.f) != n) return set_error(RLCU_ERR_INVALID, "%s is truncated", path);
             sum = fnv1a(sum, stage.data(), n);
+        }
+    }
+    uint64_t stored = 0;
+    if (fread(&stored, sizeof(stored), 1, in.f) != 1) return set_error(RLCU_ERR_INVALID, "%s is truncated (no checksum)", path);
+    if (stored != sum) return set_error(RLCU_ERR_INVALID, "%s: checksum mismatch, nothing was loaded", path);
+
+    // Second pass: the copy.  The checksum is taken again in case the file changed in between.
+    if (fseek(in.f, (long)sizeof(Header), SEEK_SET) != 0) return set_error(RLCU_ERR_INVALID, "cannot rewind %s", path);
+    cudaStream_t s = (cudaStream_t)stream;
+    float* arrays[3] = {m, v, master};
+    uint64_t sum2 = 14695981039346656037ull;
+    for (int a = 0; a < n_arrays; a++) {
+        for (size_t off = 0; off < bytes; off += kStage) {
+            const size_t n = bytes - off < kStage ? bytes - off : kStage;
+            if (fread(stage.data(), 1, n, in.f) != n) return set_error(RLCU_ERR_INVALID, "%s changed while it was read", path);
+            sum2 = fnv1a(sum2, stage.data(), n);
             RLCU_CUDA(cudaMemcpyAsync(reinterpret_cast<char*>(arrays[a]) + off, stage.data(), n,
                                       cudaMemcpyHostToDevice, s));
             RLCU_CUDA(cudaStreamSynchronize(s));
         }
     }
-    uint64_t stored = 0;
-    if (fread(&stored, sizeof(stored), 1, in.f) != 1) return set_error(RLCU_ERR_INVALID, "%s is truncated (no checksum)", path);
-    if (stored != sum) return set_error(RLCU_ERR_INVALID, "%s: checksum mismatch, the state that was loaded is corrupt", path);
+    if (sum2 != sum) return set_error(RLCU_ERR_INVALID, "%s changed while it was read; the loaded state is corrupt", path);
     if (info_out) *info_out = info;
     return RLCU_OK;
 }

@@ -12,6 +12,12 @@
 // gradients as one flat buffer (RL.cu's half_pool or float_pool), so no list and
 // no allocation are involved at any point.
 //
+// One call covers one buffer.  RL.cu's clip norm runs over two (the FP16 pool and the
+// FP32 pool, trainer.h:331-337): call once on the first buffer with RLCU_STAT_PARTIAL,
+// which leaves only its sum in the record, then on the second with RLCU_STAT_ACCUMULATE,
+// which adds its own sum to the one in the record and writes the finished record.  The
+// two calls go on the same stream, in that order.
+//
 // Cost and limits.  The array below (1 MiB + 256 B) is resident on every GPU that
 // loads the library until the process exits.  It holds one FP32 partial per 8192
 // gradient elements, which caps one call at RLCU_NOALLOC_MAX_ELEMS = 2^31
@@ -47,7 +53,8 @@ static_assert(kNoAllocMaxElems == RLCU_NOALLOC_MAX_ELEMS, "header and kernel dis
 // pointer to pass to a kernel.
 static __device__ __align__(256) float noalloc_scratch[kNoAllocSlots + 64];
 
-__device__ __forceinline__ void accum8(uint4 x, float unscale, float (&acc)[4]) {
+__device__ __forceinline__ void accum8(uint4 x, float unscale, float (&acc)[4], NanProbe& probe) {
+    probe.add_h8(x, false);
     const uint32_t w[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -61,7 +68,7 @@ __device__ __forceinline__ void accum8(uint4 x, float unscale, float (&acc)[4]) 
 // `scratch` is the device address of noalloc_scratch, resolved on the host.
 __global__ void __launch_bounds__(kThreads)
 gradstat_flat_kernel(const void* __restrict__ grad, int is_f32, int vec_ok, uint64_t n,
-                     float unscale, float max_norm, rlcu_stat* out, float* scratch) {
+                     float unscale, float max_norm, rlcu_stat* out, uint32_t flags, float* scratch) {
     __shared__ float warp_sums[kThreads / 32];
     __shared__ double warp_sums_d[kThreads / 32];
     __shared__ bool is_last;
@@ -72,11 +79,16 @@ gradstat_flat_kernel(const void* __restrict__ grad, int is_f32, int vec_ok, uint
         const uint64_t base = (uint64_t)c * kChunk;
         const uint32_t count = (uint32_t)((n - base) < (uint64_t)kChunk ? (n - base) : (uint64_t)kChunk);
         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        NanProbe probe;
         if (is_f32) {
             const float* g = static_cast<const float*>(grad) + base;
             const uint32_t quads = vec_ok ? count / 4 : 0;
             for (uint32_t q = threadIdx.x; q < quads; q += kThreads) {
                 const float4 x = __ldcs(reinterpret_cast<const float4*>(g) + q);
+                probe.add(x.x);
+                probe.add(x.y);
+                probe.add(x.z);
+                probe.add(x.w);
                 const float a0 = x.x * unscale, a1 = x.y * unscale, a2 = x.z * unscale, a3 = x.w * unscale;
                 acc[0] = fmaf(a0, a0, acc[0]);
                 acc[1] = fmaf(a1, a1, acc[1]);
@@ -84,6 +96,7 @@ gradstat_flat_kernel(const void* __restrict__ grad, int is_f32, int vec_ok, uint
                 acc[3] = fmaf(a3, a3, acc[3]);
             }
             for (uint32_t i = quads * 4 + threadIdx.x; i < count; i += kThreads) {
+                probe.add(g[i]);
                 const float x = g[i] * unscale;
                 acc[0] = fmaf(x, x, acc[0]);
             }
@@ -91,13 +104,18 @@ gradstat_flat_kernel(const void* __restrict__ grad, int is_f32, int vec_ok, uint
             const __half* g = static_cast<const __half*>(grad) + base;
             const uint32_t groups = vec_ok ? count / kGroup : 0;
             for (uint32_t grp = threadIdx.x; grp < groups; grp += kThreads)
-                accum8(ld_h8(g + (size_t)grp * kGroup), unscale, acc);
+                accum8(ld_h8(g + (size_t)grp * kGroup), unscale, acc, probe);
             for (uint32_t i = groups * kGroup + threadIdx.x; i < count; i += kThreads) {
-                const float x = __half2float(g[i]) * unscale;
+                const float raw = __half2float(g[i]);
+                probe.add(raw);
+                const float x = raw * unscale;
                 acc[0] = fmaf(x, x, acc[0]);
             }
         }
-        const float total = block_sum((acc[0] + acc[1]) + (acc[2] + acc[3]), warp_sums);
+        // an inf or NaN gradient turns the chunk's partial, and so the total, into NaN
+        float mine = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+        if (probe.bad()) mine = __int_as_float(0x7FC00000);
+        const float total = block_sum(mine, warp_sums);
         if (threadIdx.x == 0) scratch[c] = total;
         __syncthreads();                       // warp_sums is reused by the next chunk
     }
@@ -121,9 +139,17 @@ gradstat_flat_kernel(const void* __restrict__ grad, int is_f32, int vec_ok, uint
         double sum_sq = 0.0;
 #pragma unroll
         for (int w = 0; w < kThreads / 32; w++) sum_sq += warp_sums_d[w];
-        // same rule as the list-based pass: RL.cu's trainer.h:341-344
+        // a second buffer of the same step: add what the earlier RLCU_STAT_PARTIAL call left
+        if (flags & RLCU_STAT_ACCUMULATE) sum_sq += out->sum_sq;
+        if (flags & RLCU_STAT_PARTIAL) {
+            out->sum_sq = sum_sq;
+            *counter = 0;
+            return;
+        }
+        // same rule as the list-based pass: RL.cu's trainer.h:341-344; a NaN total means
+        // that some gradient was inf or NaN
         const float sf = (float)sum_sq;
-        const bool bad = !isfinite(sf);
+        const bool bad = isnan(sum_sq);
         const float norm = __fsqrt_rn(sf);
         float coef = unscale;
         uint32_t clip = 0;
@@ -183,9 +209,10 @@ int noalloc_device(NoAllocDevice* out) {
 
 extern "C" int rlcu_gradstat_flat_noalloc(const void* grad, uint32_t dtype, uint64_t n,
                                           float unscale, float max_norm,
-                                          rlcu_stat* stat_out, void* stream) {
+                                          rlcu_stat* stat_out, uint32_t flags, void* stream) {
     using namespace rlcu;
     if (!stat_out) return set_error(RLCU_ERR_INVALID, "null statistics record");
+    if (flags & ~(uint32_t)(RLCU_STAT_PARTIAL | RLCU_STAT_ACCUMULATE)) return set_error(RLCU_ERR_INVALID, "unknown flags");
     if (dtype != RLCU_F16 && dtype != RLCU_F32) return set_error(RLCU_ERR_INVALID, "unknown dtype %u", dtype);
     if (n > kNoAllocMaxElems)
         return set_error(RLCU_ERR_INVALID,
@@ -207,7 +234,7 @@ extern "C" int rlcu_gradstat_flat_noalloc(const void* grad, uint32_t dtype, uint
     // the arrival counter must start at zero whatever an earlier call left behind
     RLCU_CUDA(cudaMemsetAsync(d.scratch + kNoAllocSlots, 0, sizeof(unsigned int), s));
     gradstat_flat_kernel<<<grid, kThreads, 0, s>>>(grad, dtype == RLCU_F32, vec_ok, n, unscale, max_norm,
-                                                   stat_out, d.scratch);
+                                                   stat_out, flags, d.scratch);
     RLCU_CUDA(cudaGetLastError());
     return RLCU_OK;
 }

@@ -39,6 +39,9 @@ namespace rlcu {
 // ---------------------------------------------------------------------------
 
 // Multi-tensor update: persistent CTAs walk the work table with a grid stride.
+// GF32 = the table holds 16-bit parameters with FP32 gradients (a second instantiation, so
+// that every other list runs exactly the code it ran before that kind existed).
+template <bool GF32>
 #ifdef RLCU_MIN_CTAS
 __global__ void __launch_bounds__(kThreads, RLCU_MIN_CTAS)
 #else
@@ -61,7 +64,7 @@ adamw_table_kernel(const WorkItem* __restrict__ table, uint32_t n_items, StepCon
         const WorkItem it = next;
         const uint32_t nidx = idx + gridDim.x;
         if (nidx < n_items) next = load_item(table, nidx);   // fetched under the data loads
-        process_item<false>(it, c, xf, PeerOut{});
+        process_item<false, GF32>(it, c, xf, PeerOut{});
         if (nidx >= n_items) break;
         idx = nidx;
     }
@@ -233,7 +236,10 @@ half_to_float_kernel(float* __restrict__ dst, const __half* __restrict__ src, ui
 // ---------------------------------------------------------------------------
 
 // 1 - beta^t as the host computes it (optimizer.h:121-122: FP32 powf).  pow is
-// evaluated in FP64 and rounded once, which reproduces a correctly rounded powf.
+// evaluated in FP64 and rounded once, i.e. the correctly rounded FP32 power.  Checked
+// for beta in {0.8, 0.9, 0.95, 0.99, 0.999} and every t up to 100,000: equal to the C
+// library's powf except where that powf is itself one ulp off the correctly rounded
+// value (glibc 2.39: beta 0.999 at t = 2958 and 3606), a 6e-8 relative difference.
 __device__ __forceinline__ float bias_correction_dev(float beta, int step) {
     const float p = (float)pow((double)beta, (double)step);
     return __fsub_rn(1.0f, p);
@@ -243,8 +249,12 @@ __device__ __forceinline__ float bias_correction_dev(float beta, int step) {
 // scaler state.  Runs in one thread.
 __device__ void finalize_stat(rlcu_stat* out, double sum_sq, float unscale, float max_norm,
                               rlcu_scaler_state* scaler) {
+    // A non-finite gradient reaches this point as a NaN sum (the statistics kernels turn their
+    // partial into NaN when they see one).  An infinite sum is something else: finite
+    // gradients whose squares overflow FP32; the norm is then +inf and a clip scales the
+    // gradients to zero, which is what RL.cu's own sequence does with such values.
     const float s = (float)sum_sq;
-    const bool bad = !isfinite(s);
+    const bool bad = isnan(sum_sq);
     const float norm = __fsqrt_rn(s);                       // trainer.h:341
     float coef = unscale;
     uint32_t clip = 0;
@@ -283,7 +293,8 @@ __device__ __forceinline__ float scaler_unscale(const rlcu_scaler_state* scaler)
     return __fmul_rn(mul, __fdiv_rn(1.0f, scaler->scale));
 }
 
-__device__ __forceinline__ void accum_h8(uint4 x, float unscale, float (&acc)[4], bool bf) {
+__device__ __forceinline__ void accum_h8(uint4 x, float unscale, float (&acc)[4], bool bf, NanProbe& probe) {
+    probe.add_h8(x, bf);
     const F8 f = x8_to_f8(x, bf);
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -303,10 +314,10 @@ gradstat_kernel(const WorkItem* __restrict__ table, uint32_t n_items, float unsc
     __shared__ bool is_last;
     const float unscale = scaler ? scaler_unscale(scaler) : unscale_arg;
 
-    // Non-finite values need no separate test: inf*inf = inf and NaN propagate
-    // through the sums (squares cannot cancel), so the total is non-finite
-    // exactly when some gradient is.
+    // A thread that saw an inf or NaN gradient turns its partial into NaN, which the sums
+    // carry to the total (see NanProbe and finalize_stat).
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    NanProbe probe;
     for (uint32_t idx = blockIdx.x; idx < n_items; idx += gridDim.x) {
         // only g, count and flags are needed: words 0-1 (p,g) and 2.. (count, flags)
         const WorkItem* wi = table + idx;
@@ -317,12 +328,14 @@ gradstat_kernel(const WorkItem* __restrict__ table, uint32_t n_items, float unsc
         const uint32_t count = d.z;
         const uint32_t fl = e.x;
         if (fl & RLCU_TENSOR_GRAD_ZERO) continue;
-        const bool f32 = (fl & kItemKindMask) == kItemKindF32;
+        const bool f32 = (fl & kItemKindMask) == kItemKindF32 || (fl & kItemGradF32);
         const bool bf = (fl & kItemBF16) != 0;
         if (!(fl & kItemVec16)) {
             for (uint32_t i = threadIdx.x; i < count; i += kThreads) {
-                const float x = (f32 ? static_cast<const float*>(g)[i]
-                                     : x_to_f(static_cast<const unsigned short*>(g)[i], bf)) * unscale;
+                const float raw = f32 ? static_cast<const float*>(g)[i]
+                                      : x_to_f(static_cast<const unsigned short*>(g)[i], bf);
+                probe.add(raw);
+                const float x = raw * unscale;
                 acc[0] = fmaf(x, x, acc[0]);
             }
         } else if (!f32) {
@@ -333,13 +346,15 @@ gradstat_kernel(const WorkItem* __restrict__ table, uint32_t n_items, float unsc
                 for (int u = 0; u < kGroupsPerThread; u++)
                     x[u] = ld_h8(gh + (size_t)(threadIdx.x + u * kThreads) * kGroup);
 #pragma unroll
-                for (int u = 0; u < kGroupsPerThread; u++) accum_h8(x[u], unscale, acc, bf);
+                for (int u = 0; u < kGroupsPerThread; u++) accum_h8(x[u], unscale, acc, bf, probe);
             } else {
                 const uint32_t groups = count / kGroup;
                 for (uint32_t grp = threadIdx.x; grp < groups; grp += kThreads)
-                    accum_h8(ld_h8(gh + (size_t)grp * kGroup), unscale, acc, bf);
+                    accum_h8(ld_h8(gh + (size_t)grp * kGroup), unscale, acc, bf, probe);
                 for (uint32_t i = groups * kGroup + threadIdx.x; i < count; i += kThreads) {
-                    const float x = x_to_f(__half_as_ushort(gh[i]), bf) * unscale;
+                    const float raw = x_to_f(__half_as_ushort(gh[i]), bf);
+                    probe.add(raw);
+                    const float x = raw * unscale;
                     acc[0] = fmaf(x, x, acc[0]);
                 }
             }
@@ -348,6 +363,10 @@ gradstat_kernel(const WorkItem* __restrict__ table, uint32_t n_items, float unsc
             const uint32_t quads = count / 4;
             for (uint32_t q = threadIdx.x; q < quads; q += kThreads) {
                 const float4 x = __ldcs(reinterpret_cast<const float4*>(gf) + q);
+                probe.add(x.x);
+                probe.add(x.y);
+                probe.add(x.z);
+                probe.add(x.w);
                 const float a0 = x.x * unscale, a1 = x.y * unscale, a2 = x.z * unscale, a3 = x.w * unscale;
                 acc[0] = fmaf(a0, a0, acc[0]);
                 acc[1] = fmaf(a1, a1, acc[1]);
@@ -355,12 +374,14 @@ gradstat_kernel(const WorkItem* __restrict__ table, uint32_t n_items, float unsc
                 acc[3] = fmaf(a3, a3, acc[3]);
             }
             for (uint32_t i = quads * 4 + threadIdx.x; i < count; i += kThreads) {
+                probe.add(gf[i]);
                 const float x = gf[i] * unscale;
                 acc[0] = fmaf(x, x, acc[0]);
             }
         }
     }
-    const float mine = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    float mine = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    if (probe.bad()) mine = __int_as_float(0x7FC00000);
     const float block_total = block_sum(mine, warp_sums);
 
     if (threadIdx.x == 0) {
@@ -408,7 +429,7 @@ namespace {
 
 struct DeviceInfo {
     int sms = 0;
-    int occ_table = 0, occ_flat = 0, occ_stat = 0;
+    int occ_table = 0, occ_table_gf32 = 0, occ_flat = 0, occ_stat = 0;
 };
 
 // per-device launch geometry, looked up once per device
@@ -423,13 +444,14 @@ int device_info(DeviceInfo* out) {
     if (!have[dev]) {
         DeviceInfo di;
         RLCU_CUDA(cudaDeviceGetAttribute(&di.sms, cudaDevAttrMultiProcessorCount, dev));
-        RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&di.occ_table, adamw_table_kernel, kThreads, 0));
+        RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&di.occ_table, adamw_table_kernel<false>, kThreads, 0));
+        RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&di.occ_table_gf32, adamw_table_kernel<true>, kThreads, 0));
         RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&di.occ_flat, adamw_flat_kernel, kThreads, 0));
         RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&di.occ_stat, gradstat_kernel, kThreads, 0));
         // the bulk-copy variant needs its 192 KB ring opted in once per device
         RLCU_CUDA(cudaFuncSetAttribute(adamw_table_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kBulkSmemBytes));
-        if (di.occ_table < 1 || di.occ_flat < 1 || di.occ_stat < 1)
+        if (di.occ_table < 1 || di.occ_table_gf32 < 1 || di.occ_flat < 1 || di.occ_stat < 1)
             return set_error(RLCU_ERR_CUDA, "kernel does not fit on an SM");
         cache[dev] = di;
         have[dev] = true;
@@ -440,7 +462,11 @@ int device_info(DeviceInfo* out) {
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
-// kind and alignment bits of one tensor
+inline size_t grad_elem_size(const rlcu_tensor_desc& d) {
+    return (d.dtype == RLCU_F32 || d.grad_dtype == RLCU_GRAD_F32) ? 4 : 2;
+}
+
+// kind bits of one tensor, after checking its descriptor
 int classify(const rlcu_tensor_desc& d, uint32_t* bits) {
     uint32_t kind;
     if (d.dtype == RLCU_F32) {
@@ -451,21 +477,19 @@ int classify(const rlcu_tensor_desc& d, uint32_t* bits) {
     } else {
         return set_error(RLCU_ERR_INVALID, "unknown dtype %u", d.dtype);
     }
+    if (d.grad_dtype != RLCU_GRAD_AS_PARAM && d.grad_dtype != RLCU_GRAD_F32)
+        return set_error(RLCU_ERR_INVALID, "unknown grad_dtype %u", d.grad_dtype);
+    if (d.grad_dtype == RLCU_GRAD_F32 && d.dtype != RLCU_F32) kind |= kItemGradF32;
     const bool norm_only = d.flags & RLCU_TENSOR_NORM_ONLY;
     const bool grad_zero = d.flags & RLCU_TENSOR_GRAD_ZERO;
     if (!grad_zero && !d.grad) return set_error(RLCU_ERR_INVALID, "null gradient");
     if (!norm_only && (!d.param || !d.m || !d.v)) return set_error(RLCU_ERR_INVALID, "null param/m/v");
     const size_t esz = d.dtype == RLCU_F32 ? 4 : 2;
-    if ((d.grad && !aligned(d.grad, esz)) || (d.param && !aligned(d.param, esz)) ||
+    const size_t gesz = grad_elem_size(d);
+    if ((d.grad && !aligned(d.grad, gesz)) || (d.param && !aligned(d.param, esz)) ||
         !aligned(d.m, 4) || !aligned(d.v, 4) || !aligned(d.master, 4))
         return set_error(RLCU_ERR_INVALID, "pointer not aligned to its element size");
-    bool v16 = aligned(d.grad, 16), v32 = true;
-    if (!norm_only) {
-        v16 = v16 && aligned(d.param, 16) && aligned(d.m, 16) && aligned(d.v, 16) && aligned(d.master, 16);
-        v32 = aligned(d.m, 32) && aligned(d.v, 32) && aligned(d.master, 32);
-        if (d.dtype == RLCU_F32) v32 = v32 && aligned(d.param, 32) && aligned(d.grad, 32);
-    }
-    *bits = kind | (v16 ? kItemVec16 : 0u) | ((v16 && v32) ? kItemVec32 : 0u);
+    *bits = kind;
     return RLCU_OK;
 }
 
@@ -476,7 +500,8 @@ uint32_t item_alignment(const WorkItem& it, const rlcu_tensor_desc& d) {
     if (!norm_only) {
         v16 = v16 && aligned(it.p, 16) && aligned(it.m, 16) && aligned(it.v, 16) && aligned(it.master, 16);
         v32 = aligned(it.m, 32) && aligned(it.v, 32) && aligned(it.master, 32);
-        if (d.dtype == RLCU_F32) v32 = v32 && aligned(it.p, 32) && aligned(it.g, 32);
+        if (d.dtype == RLCU_F32) v32 = v32 && aligned(it.p, 32);
+        if (grad_elem_size(d) == 4) v32 = v32 && aligned(it.g, 32);
     }
     return (v16 ? kItemVec16 : 0u) | ((v16 && v32) ? kItemVec32 : 0u);
 }
@@ -492,7 +517,7 @@ uint64_t line_head(const rlcu_tensor_desc& d, size_t esz) {
     auto on_line = [&](const void* p, size_t sz) {
         return p == nullptr || (reinterpret_cast<uintptr_t>(p) + head * sz) % 128 == 0;
     };
-    if (!on_line(d.param, esz) || !on_line(d.grad, esz) || !on_line(d.m, 4) || !on_line(d.v, 4) ||
+    if (!on_line(d.param, esz) || !on_line(d.grad, grad_elem_size(d)) || !on_line(d.m, 4) || !on_line(d.v, 4) ||
         !on_line(d.master, 4))
         return 0;
     return head;
@@ -519,7 +544,9 @@ int launch_flat(const rlcu_tensor_desc& d, int64_t n, float lr, float b1, float 
     std::memset(&base, 0, sizeof(base));
     base.p = d.param; base.g = d.grad; base.m = d.m; base.v = d.v; base.master = d.master;
     base.wd = d.weight_decay;
-    base.flags = bits;
+    // every later item starts kChunk elements further on, which keeps whatever 16- and
+    // 32-byte alignment the tensor's first element has
+    base.flags = bits | item_alignment(base, d);
     const uint64_t items = ((uint64_t)n + kChunk - 1) / kChunk;
     const uint64_t cap = (uint64_t)di.sms * di.occ_flat;
     const int grid = (int)(items < cap ? items : cap);
@@ -608,9 +635,9 @@ int rlcu_tensor_list_create(const rlcu_tensor_desc* descs, uint64_t count, rlcu_
 
     std::vector<WorkItem> items;
     uint64_t numel = 0, stat_numel = 0;
+    bool any_grad_f32 = false;
     for (uint64_t k = 0; k < count; k++) {
         const rlcu_tensor_desc& d = descs[k];
-        if (d.reserved != 0) return set_error(RLCU_ERR_INVALID, "tensor %llu: reserved field not zero", (unsigned long long)k);
         if (d.flags & ~(uint32_t)(RLCU_TENSOR_NORM_ONLY | RLCU_TENSOR_GRAD_ZERO))
             return set_error(RLCU_ERR_INVALID, "tensor %llu: unknown flags", (unsigned long long)k);
         if (d.n == 0) continue;
@@ -620,6 +647,8 @@ int rlcu_tensor_list_create(const rlcu_tensor_desc* descs, uint64_t count, rlcu_
         if (!(d.flags & RLCU_TENSOR_NORM_ONLY)) numel += d.n;
         if (!(d.flags & RLCU_TENSOR_GRAD_ZERO)) stat_numel += d.n;
         const size_t esz = d.dtype == RLCU_F32 ? 4 : 2;
+        const size_t gesz = grad_elem_size(d);
+        if (bits & kItemGradF32) any_grad_f32 = true;
         // Work items are cut so that, from the second one on, every pointer sits on a
         // 128-byte line: a tensor that starts in the middle of a line (ragged sizes packed
         // into one arena) gets a short head item first.  Without this a warp's accesses
@@ -631,13 +660,13 @@ int rlcu_tensor_list_create(const rlcu_tensor_desc* descs, uint64_t count, rlcu_
             WorkItem it;
             std::memset(&it, 0, sizeof(it));
             it.p = d.param ? static_cast<char*>(d.param) + off * esz : nullptr;
-            it.g = d.grad ? static_cast<const char*>(d.grad) + off * esz : nullptr;
+            it.g = d.grad ? static_cast<const char*>(d.grad) + off * gesz : nullptr;
             it.m = d.m ? d.m + off : nullptr;
             it.v = d.v ? d.v + off : nullptr;
             it.master = d.master ? d.master + off : nullptr;
             it.count = (uint32_t)((d.n - off) < want ? (d.n - off) : want);
             it.wd = d.weight_decay;
-            it.flags = d.flags | (bits & (kItemKindMask | kItemBF16)) | item_alignment(it, d);
+            it.flags = d.flags | (bits & (kItemKindMask | kItemBF16 | kItemGradF32)) | item_alignment(it, d);
             items.push_back(it);
             off += it.count;
         }
@@ -650,7 +679,8 @@ int rlcu_tensor_list_create(const rlcu_tensor_desc* descs, uint64_t count, rlcu_
     L->n_items = (uint32_t)items.size();
     L->numel = numel;
     L->stat_numel = stat_numel;
-    const uint64_t cap_u = (uint64_t)di.sms * di.occ_table, cap_s = (uint64_t)di.sms * di.occ_stat;
+    L->has_grad_f32 = any_grad_f32;
+    const uint64_t cap_u = (uint64_t)di.sms * (any_grad_f32 ? di.occ_table_gf32 : di.occ_table), cap_s = (uint64_t)di.sms * di.occ_stat;
     L->grid_update = (int)(L->n_items < cap_u ? (L->n_items ? L->n_items : 1) : cap_u);
     L->grid_stat = (int)(L->n_items < cap_s ? (L->n_items ? L->n_items : 1) : cap_s);
 
@@ -690,6 +720,9 @@ int rlcu_tensor_list_destroy(rlcu_tensor_list* list) {
 int rlcu_tensor_list_check(rlcu_tensor_list* list) {
     if (!list) return set_error(RLCU_ERR_INVALID, "null list");
     unsigned int word = 0;
+    // A blocking copy on the legacy stream does not wait for streams created with
+    // cudaStreamNonBlocking, so wait for the whole device first.
+    RLCU_CUDA(cudaDeviceSynchronize());
     RLCU_CUDA(cudaMemcpy(&word, list->d_counter + 16, sizeof(word), cudaMemcpyDeviceToHost));
     if (word) {
         cudaMemset(list->d_counter + 16, 0, sizeof(word));
@@ -739,6 +772,8 @@ int rlcu_adamw_multi_step(rlcu_tensor_list* list, const rlcu_hparams* hp,
         return set_error(RLCU_ERR_INVALID, "device bias correction needs a statistics record");
     if (list->n_items == 0) return RLCU_OK;
     if (step_flags & RLCU_STEP_BULK_COPY) {
+        if (list->has_grad_f32)
+            return set_error(RLCU_ERR_UNSUPPORTED, "the bulk-copy update does not take FP32 gradients for 16-bit parameters");
         DeviceInfo di;
         const int rc = device_info(&di);
         if (rc) return rc;
@@ -750,10 +785,14 @@ int rlcu_adamw_multi_step(rlcu_tensor_list* list, const rlcu_hparams* hp,
         RLCU_CUDA(cudaGetLastError());
         return RLCU_OK;
     }
-    adamw_table_kernel<<<list->grid_update, kThreads, 0, (cudaStream_t)stream>>>(
-        list->d_items, list->n_items,
-        make_consts(hp->lr, hp->beta1, hp->beta2, hp->eps, hp->bias_correction1, hp->bias_correction2),
-        stat, step_flags);
+    const StepConsts consts =
+        make_consts(hp->lr, hp->beta1, hp->beta2, hp->eps, hp->bias_correction1, hp->bias_correction2);
+    if (list->has_grad_f32)
+        adamw_table_kernel<true><<<list->grid_update, kThreads, 0, (cudaStream_t)stream>>>(
+            list->d_items, list->n_items, consts, stat, step_flags);
+    else
+        adamw_table_kernel<false><<<list->grid_update, kThreads, 0, (cudaStream_t)stream>>>(
+            list->d_items, list->n_items, consts, stat, step_flags);
     RLCU_CUDA(cudaGetLastError());
     return RLCU_OK;
 }

@@ -173,12 +173,39 @@ int barrier(rlcu_zero1* z, cudaStream_t s) {
     return RLCU_OK;
 }
 
-// Maps every peer's gradient and parameter pool into this process.  Collective.
+// Collective: every rank reports whether its own preparation worked (`local_rc`), and all
+// return an error if any rank failed, so that no rank goes on to a collective the others
+// will never join.  Needs only the communicator and z->d_barrier (which may be null on a
+// rank whose allocation failed: that rank then cannot take part, and says so by aborting
+// the communicator, which ends the others' wait with an error instead of a hang).
+int agree(rlcu_zero1* z, int local_rc, const char* what) {
+    if (!z->d_barrier) {
+        z->api->CommAbort(z->comm);
+        z->comm = nullptr;
+        return local_rc ? local_rc : set_error(RLCU_ERR_CUDA, "%s: no device memory for the agreement word", what);
+    }
+    int flag = local_rc ? 1 : 0;
+    cudaError_t ce = cudaMemcpy(z->d_barrier, &flag, sizeof(int), cudaMemcpyHostToDevice);
+    ncclResult_t nr = ncclSuccess;
+    if (ce == cudaSuccess) {
+        nr = z->api->AllReduce(z->d_barrier, z->d_barrier, 1, ncclInt32, ncclSum, z->comm, 0);
+        ce = cudaStreamSynchronize(0);
+    }
+    int failed = 1;
+    if (nr == ncclSuccess && ce == cudaSuccess) ce = cudaMemcpy(&failed, z->d_barrier, sizeof(int), cudaMemcpyDeviceToHost);
+    cudaMemset(z->d_barrier, 0, 256);
+    if (local_rc) return local_rc;                       // this rank's own message stays in place
+    if (nr != ncclSuccess) return set_error(RLCU_ERR_NCCL, "%s: %s", what, z->api->GetErrorString(nr));
+    if (ce != cudaSuccess) return set_error(RLCU_ERR_CUDA, "%s: %s", what, cudaGetErrorString(ce));
+    if (failed) return set_error(RLCU_ERR_CUDA, "%s: another rank failed", what);
+    return RLCU_OK;
+}
+
+// Maps every peer's gradient and parameter pool into this process.  Collective; no early
+// return before a collective the other ranks take part in.
 int setup_p2p(rlcu_zero1* z) {
     const int W = z->world;
     if (W > rlcu::kMaxWorld) return set_error(RLCU_ERR_UNSUPPORTED, "peer-to-peer mode supports at most %d ranks", rlcu::kMaxWorld);
-    RLCU_CUDA(cudaMalloc(&z->d_barrier, 256));
-    RLCU_CUDA(cudaMemset(z->d_barrier, 0, 256));
 
     PoolExport mine{};
     void *gbase = nullptr, *pbase = nullptr;
@@ -195,9 +222,15 @@ int setup_p2p(rlcu_zero1* z) {
     mine.param_offset = ok ? (uint64_t)((char*)z->param_pool - (char*)pbase) : 0;
     mine.ok = ok ? 1 : 0;
 
-    std::vector<PoolExport> all(W);
     PoolExport* d_all = nullptr;
-    RLCU_CUDA(cudaMalloc(&d_all, sizeof(PoolExport) * W));
+    const cudaError_t alloc_e = cudaMalloc(&d_all, sizeof(PoolExport) * W);
+    rc = agree(z, alloc_e == cudaSuccess ? RLCU_OK : set_error(RLCU_ERR_CUDA, "handle exchange buffer: %s", cudaGetErrorString(alloc_e)),
+               "handle exchange set-up");
+    if (rc) {
+        cudaFree(d_all);
+        return rc;
+    }
+    std::vector<PoolExport> all(W);
     cudaError_t ce = cudaMemcpy(d_all + z->rank, &mine, sizeof(PoolExport), cudaMemcpyHostToDevice);
     ncclResult_t nr = ncclSuccess;
     if (ce == cudaSuccess) {
@@ -242,17 +275,7 @@ int setup_p2p(rlcu_zero1* z) {
         z->params_out.base[z->params_out.n++] = reinterpret_cast<__half*>((char*)p + all[j].param_offset);
     }
     // every rank must agree that the mapping worked before anyone relies on it
-    int flag = opened_all ? 0 : 1;
-    RLCU_CUDA(cudaMemcpy(z->d_barrier, &flag, sizeof(int), cudaMemcpyHostToDevice));
-    nr = z->api->AllReduce(z->d_barrier, z->d_barrier, 1, ncclInt32, ncclSum, z->comm, 0);
-    ce = cudaStreamSynchronize(0);
-    int failed = 1;
-    if (nr == ncclSuccess && ce == cudaSuccess) ce = cudaMemcpy(&failed, z->d_barrier, sizeof(int), cudaMemcpyDeviceToHost);
-    cudaMemset(z->d_barrier, 0, 256);
-    if (nr != ncclSuccess) return set_error(RLCU_ERR_NCCL, "mapping agreement: %s", z->api->GetErrorString(nr));
-    if (ce != cudaSuccess) return set_error(RLCU_ERR_CUDA, "mapping agreement: %s", cudaGetErrorString(ce));
-    if (failed) return opened_all ? set_error(RLCU_ERR_CUDA, "another rank could not map the pools") : RLCU_ERR_CUDA;
-    return RLCU_OK;
+    return agree(z, opened_all ? RLCU_OK : RLCU_ERR_CUDA, "mapping the peers' pools");
 }
 
 void release_p2p(rlcu_zero1* z) {
@@ -317,10 +340,6 @@ int rlcu_zero1_create(const void* unique_id, int rank, int world,
         return set_error(RLCU_ERR_INVALID, "null pointer");
     int rc = check_geometry(segs, nsegs, rank, world);
     if (rc) return rc;
-    if (reinterpret_cast<uintptr_t>(param_pool) % 16 || reinterpret_cast<uintptr_t>(grad_pool) % 16 ||
-        reinterpret_cast<uintptr_t>(m_shard) % 32 || reinterpret_cast<uintptr_t>(v_shard) % 32 ||
-        reinterpret_cast<uintptr_t>(master_shard) % 32)
-        return set_error(RLCU_ERR_INVALID, "pools must be 16-byte aligned, shard state 32-byte aligned");
     const NcclApi* api;
     rc = nccl_api(&api);
     if (rc) return rc;
@@ -351,28 +370,35 @@ int rlcu_zero1_create(const void* unique_id, int rank, int world,
         d.flags = p.flags;
         descs.push_back(d);
     }
-    rc = rlcu_tensor_list_create(descs.data(), descs.size(), &z->list);
-    if (rc) {
-        delete z;
-        return rc;
-    }
+    // Join the communicator before any rank-local work that can fail: a rank that returned
+    // early would leave the others waiting in ncclCommInitRank for good.
     ncclUniqueId id;
     memcpy(&id, unique_id, sizeof(id));
     ncclResult_t nr = api->CommInitRank(&z->comm, world, id, rank);
     if (nr != ncclSuccess) {
-        rlcu_tensor_list_destroy(z->list);
         delete z;
         return set_error(RLCU_ERR_NCCL, "ncclCommInitRank: %s", api->GetErrorString(nr));
     }
-    if (mode == RLCU_ZERO1_P2P) {
-        rc = setup_p2p(z);
-        if (rc) {
-            release_p2p(z);
-            api->CommAbort(z->comm);
-            rlcu_tensor_list_destroy(z->list);
-            delete z;
-            return rc;
-        }
+    // Rank-local checks and set-up, then every rank learns whether all of them got through.
+    if (reinterpret_cast<uintptr_t>(param_pool) % 16 || reinterpret_cast<uintptr_t>(grad_pool) % 16 ||
+        reinterpret_cast<uintptr_t>(m_shard) % 32 || reinterpret_cast<uintptr_t>(v_shard) % 32 ||
+        reinterpret_cast<uintptr_t>(master_shard) % 32)
+        rc = set_error(RLCU_ERR_INVALID, "pools must be 16-byte aligned, shard state 32-byte aligned");
+    else
+        rc = rlcu_tensor_list_create(descs.data(), descs.size(), &z->list);
+    if (cudaMalloc(&z->d_barrier, 256) != cudaSuccess || cudaMemset(z->d_barrier, 0, 256) != cudaSuccess) {
+        if (!rc) rc = set_error(RLCU_ERR_CUDA, "agreement word: %s", cudaGetErrorString(cudaGetLastError()));
+        if (z->d_barrier) cudaFree(z->d_barrier);
+        z->d_barrier = nullptr;
+    }
+    rc = agree(z, rc, "sharded step set-up");
+    if (!rc && mode == RLCU_ZERO1_P2P) rc = setup_p2p(z);
+    if (rc) {
+        release_p2p(z);
+        if (z->comm) api->CommAbort(z->comm);
+        rlcu_tensor_list_destroy(z->list);
+        delete z;
+        return rc;
     }
     *out = z;
     return RLCU_OK;
@@ -391,6 +417,11 @@ int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float 
     // ones to the division); 1/world goes into the factor applied in registers
     const float unscale_all = unscale / (float)z->world;
     int rc;
+    const uint32_t known_flags = RLCU_STEP_ROUND_CLIP_FP16 | RLCU_STEP_DEVICE_BIAS_CORRECTION | RLCU_STEP_ZERO_GRADS;
+    if (step_flags & ~known_flags)
+        return set_error(RLCU_ERR_INVALID, "step flags 0x%x are not available in the sharded step", step_flags & ~known_flags);
+    if ((step_flags & RLCU_STEP_DEVICE_BIAS_CORRECTION) && !scaler)
+        return set_error(RLCU_ERR_INVALID, "device bias correction needs a scaler state");
     if (z->mode == RLCU_ZERO1_P2P) {
         if (step_flags & RLCU_STEP_ZERO_GRADS)
             return set_error(RLCU_ERR_UNSUPPORTED, "RLCU_STEP_ZERO_GRADS is not available in the sharded step");

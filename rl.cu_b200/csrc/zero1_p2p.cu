@@ -30,9 +30,12 @@ __device__ __forceinline__ void add_h8(uint4 x, F8& acc, bool bf) {
     for (int i = 0; i < 8; i++) acc.a[i] = __fadd_rn(acc.a[i], f.a[i]);
 }
 
-__device__ __forceinline__ void square_accumulate(const F8& x, float unscale, float (&acc)[4]) {
+// x holds the reduced gradients as stored (already rounded to 16 bits): they are what the
+// update will use, so a sum that overflowed the 16-bit format counts as non-finite.
+__device__ __forceinline__ void square_accumulate(const F8& x, float unscale, float (&acc)[4], float& probe) {
 #pragma unroll
     for (int i = 0; i < 8; i++) {
+        probe = __fmaf_rn(x.a[i], 0.0f, probe);        // NaN once any value is inf or NaN
         const float a = x.a[i] * unscale;
         acc[i & 3] = fmaf(a, a, acc[i & 3]);
     }
@@ -43,7 +46,8 @@ __device__ __forceinline__ void square_accumulate(const F8& x, float unscale, fl
 // once to FP16.  Group u of the thread is `stride` groups after group u-1.
 template <int WORLD, int UB>
 __device__ __forceinline__ void reduce_groups(const PeerIn& peers, ptrdiff_t off, __half* dst,
-                                              ptrdiff_t stride, float unscale, float (&acc)[4], bool bf) {
+                                              ptrdiff_t stride, float unscale, float (&acc)[4], bool bf,
+                                              float& probe) {
     constexpr int W = WORLD > 0 ? WORLD : kMaxWorld;
     const int n = WORLD > 0 ? WORLD : peers.n;
     uint4 x[UB][W];
@@ -60,7 +64,7 @@ __device__ __forceinline__ void reduce_groups(const PeerIn& peers, ptrdiff_t off
             if (j < n) add_h8(x[u][j], sum, bf);
         const uint4 r = f8_to_x8(sum, bf);
         *reinterpret_cast<uint4*>(dst + u * stride * kGroup) = r;   // default policy: the update pass reads it next
-        square_accumulate(x8_to_f8(r, bf), unscale, acc);
+        square_accumulate(x8_to_f8(r, bf), unscale, acc, probe);
     }
 }
 
@@ -76,7 +80,8 @@ __device__ __forceinline__ U8 ld_h16(const __half* p) {
 // 16 consecutive elements per thread with 256-bit loads from every rank.
 template <int WORLD, int UB>
 __device__ __forceinline__ void reduce_wide(const PeerIn& peers, ptrdiff_t off, __half* dst,
-                                            ptrdiff_t stride, float unscale, float (&acc)[4], bool bf) {
+                                            ptrdiff_t stride, float unscale, float (&acc)[4], bool bf,
+                                            float& probe) {
     constexpr int W = WORLD > 0 ? WORLD : kMaxWorld;
     const int n = WORLD > 0 ? WORLD : peers.n;
     U8 x[UB][W];
@@ -95,7 +100,7 @@ __device__ __forceinline__ void reduce_wide(const PeerIn& peers, ptrdiff_t off, 
                 if (j < n) add_h8(make_uint4(x[u][j].w[4 * h], x[u][j].w[4 * h + 1], x[u][j].w[4 * h + 2], x[u][j].w[4 * h + 3]), sum, bf);
             const uint4 r = f8_to_x8(sum, bf);
             *reinterpret_cast<uint4*>(dst + u * stride * 16 + h * 8) = r;
-            square_accumulate(x8_to_f8(r, bf), unscale, acc);
+            square_accumulate(x8_to_f8(r, bf), unscale, acc, probe);
         }
     }
 }
@@ -106,8 +111,11 @@ struct ReduceBatch {
     static constexpr int value = WORLD == 1 ? 4 : WORLD == 2 ? 4 : WORLD == 4 ? 2 : 1;
 };
 
+// The kernel waits on NVLink round trips, so residency matters more than registers: the
+// 4-rank instantiation is held to the register count that lets three CTAs share an SM
+// (a minimum of 0 leaves the others to the compiler).
 template <int WORLD>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, WORLD == 4 ? 3 : 0)
 reduce_stat_kernel(const WorkItem* __restrict__ table, uint32_t n_items,
                    const __grid_constant__ PeerIn peers, float unscale_arg,
                    const rlcu_scaler_state* scaler, rlcu_stat* out, float* partials,
@@ -121,6 +129,7 @@ reduce_stat_kernel(const WorkItem* __restrict__ table, uint32_t n_items,
     }
     const int n = WORLD > 0 ? WORLD : peers.n;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float probe = 0.0f;
     for (uint32_t idx = blockIdx.x; idx < n_items; idx += gridDim.x) {
         const WorkItem* wi = table + idx;
         const uint4 a = __ldg(reinterpret_cast<const uint4*>(wi));        // p, g
@@ -143,7 +152,7 @@ reduce_stat_kernel(const WorkItem* __restrict__ table, uint32_t n_items,
 #pragma unroll
             for (int b = 0; b < 2 / UB; b++) {
                 const ptrdiff_t first = (ptrdiff_t)(threadIdx.x + b * UB * kThreads) * 16;
-                reduce_wide<WORLD, UB>(peers, base_off + first, g + first, kThreads, unscale, acc, bf);
+                reduce_wide<WORLD, UB>(peers, base_off + first, g + first, kThreads, unscale, acc, bf, probe);
             }
             continue;
         }
@@ -152,22 +161,26 @@ reduce_stat_kernel(const WorkItem* __restrict__ table, uint32_t n_items,
 #pragma unroll
             for (int b = 0; b < kGroupsPerThread / UB; b++) {
                 const ptrdiff_t first = (ptrdiff_t)(threadIdx.x + b * UB * kThreads) * kGroup;
-                reduce_groups<WORLD, UB>(peers, base_off + first, g + first, kThreads, unscale, acc, bf);
+                reduce_groups<WORLD, UB>(peers, base_off + first, g + first, kThreads, unscale, acc, bf, probe);
             }
             continue;
         }
         for (uint32_t grp = threadIdx.x; grp < groups; grp += kThreads)
-            reduce_groups<WORLD, 1>(peers, base_off + (ptrdiff_t)grp * kGroup, g + (size_t)grp * kGroup, 0, unscale, acc, bf);
+            reduce_groups<WORLD, 1>(peers, base_off + (ptrdiff_t)grp * kGroup, g + (size_t)grp * kGroup, 0, unscale, acc, bf, probe);
         for (uint32_t i = groups * kGroup + threadIdx.x; i < count; i += kThreads) {
             float s = x_to_f(__half_as_ushort(peers.base[0][base_off + i]), bf);
             for (int j = 1; j < n; j++) s = __fadd_rn(s, x_to_f(__half_as_ushort(peers.base[j][base_off + i]), bf));
             const __half r = __ushort_as_half(f_to_x(s, bf));
             g[i] = r;
-            const float x = x_to_f(__half_as_ushort(r), bf) * unscale;
+            const float raw = x_to_f(__half_as_ushort(r), bf);
+            probe = __fmaf_rn(raw, 0.0f, probe);
+            const float x = raw * unscale;
             acc[0] = fmaf(x, x, acc[0]);
         }
     }
-    const float block_total = block_sum((acc[0] + acc[1]) + (acc[2] + acc[3]), warp_sums);
+    float mine = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    if (isnan(probe)) mine = __int_as_float(0x7FC00000);     // NaN total = a non-finite gradient (see finalize_stat)
+    const float block_total = block_sum(mine, warp_sums);
     if (threadIdx.x == 0) {
         partials[blockIdx.x] = block_total;
         __threadfence();

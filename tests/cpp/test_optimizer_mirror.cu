@@ -163,6 +163,54 @@ int main() {
         EXPECT(moved.get_step() == 4, "move construction keeps state and step counter");
     }
 
+    // ---- weight_decay is a public field: a change between steps takes effect, as in RL.cu,
+    //      which hands the field to the launcher on every step (optimizer.h:126-129)
+    upload();
+    {
+        AdamWOptimizer opt(&model, 1e-3f, 0.9f, 0.999f, 1e-8f, 0.01f);
+        opt.step(&grads);
+        opt.weight_decay = 0.1f;
+        opt.step(&grads);
+        CUDA_CHECK(cudaDeviceSynchronize());
+        auto p_b = download(model.weights.fp16_pool, n16);
+        auto master_b = download(opt.fp16_master(), n16);
+        upload();
+        float *master, *m, *v;
+        CUDA_CHECK(cudaMalloc(&master, n16 * 4)); CUDA_CHECK(cudaMalloc(&m, n16 * 4)); CUDA_CHECK(cudaMalloc(&v, n16 * 4));
+        CUDA_CHECK(cudaMemset(m, 0, n16 * 4)); CUDA_CHECK(cudaMemset(v, 0, n16 * 4));
+        std::vector<float> mh(n16);
+        for (size_t i = 0; i < n16; i++) mh[i] = __half2float(w16[i]);
+        CUDA_CHECK(cudaMemcpy(master, mh.data(), n16 * 4, cudaMemcpyHostToDevice));
+        const float wds[2] = {0.01f, 0.1f};
+        for (int s = 1; s <= 2; s++) {
+            const float bc1 = 1.0f - powf(0.9f, (float)s), bc2 = 1.0f - powf(0.999f, (float)s);
+            launch_adamw_fp16(master, model.weights.fp16_pool, grads.half_pool, m, v, (int)proj_n,
+                              1e-3f, 0.9f, 0.999f, 1e-8f, wds[s - 1], bc1, bc2);
+            launch_adamw_fp16(master + proj_n, model.weights.fp16_pool + proj_n, grads.half_pool + proj_n,
+                              m + proj_n, v + proj_n, (int)(n16 - proj_n), 1e-3f, 0.9f, 0.999f, 1e-8f, 0.0f, bc1, bc2);
+        }
+        CUDA_CHECK(cudaDeviceSynchronize());
+        EXPECT(same(p_b, download(model.weights.fp16_pool, n16)) && same(master_b, download(master, n16)),
+               "weight_decay changed between steps is honoured");
+        cudaFree(master); cudaFree(m); cudaFree(v);
+    }
+
+    // ---- a step with a non-finite gradient writes nothing and does not count
+    upload();
+    {
+        AdamWOptimizer opt(&model, 1e-3f);
+        opt.clip_and_step(&grads, 1.0f);
+        auto p_before = download(model.weights.fp16_pool, n16);
+        const half inf = __float2half(INFINITY);
+        CUDA_CHECK(cudaMemcpy(grads.half_pool + 5, &inf, sizeof(half), cudaMemcpyHostToDevice));
+        opt.clip_and_step_async(&grads, 1.0f);
+        EXPECT(opt.last_step_skipped() && opt.get_step() == 1, "skipped step leaves the step counter");
+        EXPECT(same(p_before, download(model.weights.fp16_pool, n16)), "skipped step leaves the weights");
+        CUDA_CHECK(cudaMemcpy(grads.half_pool + 5, &g16[5], sizeof(half), cudaMemcpyHostToDevice));
+        opt.clip_and_step(&grads, 1.0f);
+        EXPECT(!opt.last_step_skipped() && opt.get_step() == 2, "the next clean step is step 2");
+    }
+
     printf("%d failure(s)\n", failures);
     return failures;
 }

@@ -3,7 +3,20 @@ guard words, descriptor construction, and comparison in the units the parity
 bars are stated in (FP16 ulps, relative FP32 error)."""
 from __future__ import annotations
 
+import os
+
 import numpy as np
+
+
+def reference_checkout():
+    """Path of a checkout of KJLdefeated/RL.cu, or None: the directory RLCU_REFERENCE names,
+    else a directory called ``reference`` beside this repository."""
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for cand in (os.environ.get("RLCU_REFERENCE"), os.path.join(os.path.dirname(here), "reference")):
+        if cand and os.path.exists(os.path.join(cand, "src", "kernels", "adamw.cu")):
+            return cand
+    return None
+
 
 GUARD = 64          # guard elements before and after every device buffer
 GUARD_BYTE = 0x5A

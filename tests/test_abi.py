@@ -52,7 +52,7 @@ def test_struct_layouts(pkg):
     assert C.sizeof(pkg.HParams) == 24
     assert pkg.TensorDesc.n.offset == 40 and pkg.TensorDesc.flags.offset == 56
     assert pkg.Stat.coef.offset == 12 and pkg.Stat.found_inf.offset == 16
-    assert pkg.lib().rlcu_abi_version() == 1
+    assert pkg.lib().rlcu_abi_version() == 2
 
 
 def test_bias_correction_host_helper(pkg, O):

@@ -42,6 +42,21 @@ def test_empty_state_round_trip_on_the_host(pkg, tmp_path):
     assert again.step == 17
 
 
+def test_failed_save_keeps_the_previous_checkpoint(pkg, tmp_path):
+    """The file is written beside the target and renamed over it when complete: a save that
+    cannot finish (here: the temporary name is taken by a directory) leaves the old file alone."""
+    path = tmp_path / "opt.ckpt"
+    pkg.checkpoint_save(path, pkg.CheckpointInfo(0, 3, 1024.0, 0, 0, 0, 1, 0, 0), None, None)
+    old = path.read_bytes()
+    (tmp_path / "opt.ckpt.tmp").mkdir()
+    with pytest.raises(pkg.RlcuError):
+        pkg.checkpoint_save(path, pkg.CheckpointInfo(0, 4, 2048.0, 0, 0, 0, 1, 0, 0), None, None)
+    assert path.read_bytes() == old and pkg.checkpoint_peek(path).step == 3
+    (tmp_path / "opt.ckpt.tmp").rmdir()
+    pkg.checkpoint_save(path, pkg.CheckpointInfo(0, 4, 2048.0, 0, 0, 0, 1, 0, 0), None, None)
+    assert pkg.checkpoint_peek(path).step == 4 and not (tmp_path / "opt.ckpt.tmp").exists()
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("with_master", [False, True])
 def test_resume_is_bit_identical(pkg, O, tmp_path, with_master):
@@ -100,10 +115,20 @@ def test_resume_is_bit_identical(pkg, O, tmp_path, with_master):
     with pytest.raises(pkg.RlcuError):
         pkg.checkpoint_load(path, b["m"].data_ptr(), b["v"].data_ptr(),
                             None if with_master else b["m"].data_ptr(), n)
-    raw = bytearray(path.read_bytes())
+    # a corrupt or truncated file is refused before anything reaches the live state
+    good = path.read_bytes()
+    raw = bytearray(good)
     raw[128 + 1000] ^= 0x40
     path.write_bytes(bytes(raw))
+    before = {k: b[k].clone() for k in ("m", "v", "master") if b[k] is not None}
     with pytest.raises(pkg.RlcuError) as e:
         pkg.checkpoint_load(path, b["m"].data_ptr(), b["v"].data_ptr(),
                             b["master"].data_ptr() if with_master else None, n)
     assert "checksum" in str(e.value)
+    path.write_bytes(good[:len(good) // 2])
+    with pytest.raises(pkg.RlcuError) as e:
+        pkg.checkpoint_load(path, b["m"].data_ptr(), b["v"].data_ptr(),
+                            b["master"].data_ptr() if with_master else None, n)
+    assert "truncated" in str(e.value)
+    for k, t in before.items():
+        assert torch.equal(t.view(torch.int32), b[k].view(torch.int32)), f"{k} was touched by a refused load"

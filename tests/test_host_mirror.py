@@ -1,7 +1,7 @@
 """The C++ AdamWOptimizer mirror (include/training/optimizer.h).
 
 CPU: it compiles against a stand-in for RL.cu's model header, and -- when a checkout of RL.cu
-is found at the path in RLCU_REFERENCE (or the default below) -- RL.cu's own tests/test_adamw.cu compiles
+is found (RLCU_REFERENCE, or a directory named "reference" beside this repository) -- RL.cu's own tests/test_adamw.cu compiles
 unchanged against it.  GPU: the mirror's test program runs and reports no failure."""
 import os
 import shutil
@@ -9,9 +9,11 @@ import subprocess
 
 import pytest
 
+from helpers import reference_checkout
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CPP = os.path.join(ROOT, "tests", "cpp")
-REF = os.environ.get("RLCU_REFERENCE", "/root/reference")
+REF = reference_checkout() or ""
 NVCC = ["nvcc", "-std=c++17", "-O2", "--expt-relaxed-constexpr", "-gencode", "arch=compute_100a,code=sm_100a"]
 
 
@@ -49,7 +51,7 @@ def test_mirror_program_passes_on_the_gpu(mirror_binary):
     r = subprocess.run([mirror_binary], capture_output=True, text=True)
     print(r.stdout)
     assert r.returncode == 0, r.stdout + r.stderr
-    assert "[FAIL]" not in r.stdout and r.stdout.count("[PASS]") >= 13
+    assert "[FAIL]" not in r.stdout and r.stdout.count("[PASS]") >= 17
 
 
 def test_reference_test_binary_links_against_the_library(pkg, tmp_path):
@@ -84,6 +86,54 @@ def test_reference_test_binary_links_against_the_library(pkg, tmp_path):
         assert sym in undefined, f"{sym} is not taken from the shared library"
     needed = subprocess.run(["ldd", exe], check=True, capture_output=True, text=True).stdout
     assert "librlcu_b200.so" in needed
+
+
+@pytest.mark.parametrize("program", ["train_sft", "train_grpo"])
+def test_reference_trainers_compile_with_the_fused_step_patch(tmp_path, program):
+    """The trainer side of the drop-in: include/training/trainer_fused_step.patch, applied to
+    copies of RL.cu's trainer.h and GRPO_trainer.h, replaces clip_grad_norm_ + optimizer_.step
+    (trainer.h:279-286, GRPO_trainer.h:507-514) and the freeze_embed memset (trainer.h:271-277)
+    by AdamWOptimizer::clip_and_step of this repository's optimizer.h.  RL.cu's own
+    tests/train_sft.cu and tests/train_grpo.cu then compile, call the fused library entry
+    points, and no longer contain RL.cu's sum-of-squares and scale kernels."""
+    import glob
+    import sysconfig
+    src = os.path.join(REF, "tests", f"{program}.cu")
+    if not os.path.exists(src) or shutil.which("nvcc") is None or shutil.which("patch") is None:
+        pytest.skip("no checkout of RL.cu here")
+    site = sysconfig.get_paths()["purelib"]
+    json_hpp = glob.glob(os.path.join(site, "include", "cudnn_frontend", "thirdparty", "nlohmann", "json.hpp"))
+    xxhash_h = glob.glob(os.path.join(site, "pyarrow", "include", "arrow", "vendored", "xxhash", "xxhash.h"))
+    if not json_hpp or not xxhash_h:
+        pytest.skip("nlohmann/json or xxhash, which RL.cu expects under third_party/, is not installed")
+    shim = tmp_path / "shim" / "third_party"
+    shim.mkdir(parents=True)
+    os.symlink(json_hpp[0], shim / "json.hpp")
+    os.symlink(xxhash_h[0], shim / "xxhash.h")
+    # a training/ directory that is RL.cu's, with the two patched headers and this repository's optimizer.h
+    tdir = tmp_path / "patched" / "include" / "training"
+    tdir.mkdir(parents=True)
+    ref_training = os.path.join(REF, "include", "training")
+    for name in os.listdir(ref_training):
+        if name in ("trainer.h", "GRPO_trainer.h"):
+            shutil.copy(os.path.join(ref_training, name), tdir / name)
+            os.chmod(tdir / name, 0o644)
+        elif name == "optimizer.h":
+            os.symlink(os.path.join(ROOT, "include", "training", "optimizer.h"), tdir / name)
+        else:
+            os.symlink(os.path.join(ref_training, name), tdir / name)
+    with open(os.path.join(ROOT, "include", "training", "trainer_fused_step.patch")) as patch:
+        subprocess.run(["patch", "-p1", "-d", str(tmp_path / "patched")], stdin=patch, check=True)
+    obj = str(tmp_path / f"{program}.o")
+    cmd = ["nvcc", "-std=c++17", "-O0", "--expt-relaxed-constexpr", "-w", "-gencode", "arch=compute_100a,code=sm_100a",
+           "-I", os.path.join(ROOT, "include"), "-I", str(tmp_path / "patched" / "include"),
+           "-I", os.path.join(REF, "include"), "-I", str(tmp_path / "shim"), "-c", src, "-o", obj]
+    subprocess.run(cmd, check=True)
+    syms = subprocess.run(["nm", "-C", obj], check=True, capture_output=True, text=True).stdout
+    for wanted in ("U rlcu_gradstat", "U rlcu_adamw_multi_step", "clip_and_step"):
+        assert wanted in syms, wanted
+    for gone in ("sum_sq_half_kernel", "sum_sq_float_kernel", "scale_half_kernel", "clip_grad_norm_", "launch_adamw_fp16"):
+        assert gone not in syms, gone
 
 
 @pytest.fixture(scope="module")

@@ -23,8 +23,9 @@ def torch():
 
 
 def make_case(O, torch, pkg, specs, seed, g_std=1e-2, offset=0):
-    """specs: list of (n, kind, wd, flags) with kind in {'h', 'hm', 'f'}.  Returns the host
-    entries (oracle side), device buffers and the product's descriptors."""
+    """specs: list of (n, kind, wd, flags) with kind in {'h', 'hm', 'f', 'hg', 'hmg'}: FP16,
+    FP16 with FP32 master, FP32, and the two FP16 kinds with an FP32 gradient.  Returns the
+    host entries (oracle side), device buffers and the product's descriptors."""
     host, dev, descs = [], [], []
     for k, (n, kind, wd, flags) in enumerate(specs):
         p, g, m, v = seeded_case(O, n, seed=[seed, k], g_std=g_std, warm=True)
@@ -33,14 +34,20 @@ def make_case(O, torch, pkg, specs, seed, g_std=1e-2, offset=0):
             e.update(p=O.h2f(p), g=O.h2f(g), m=m, v=v)
         else:
             e.update(p=p, g=g, m=m, v=v)
-            if kind == "hm":
+            if kind in ("hm", "hmg"):
                 e["master"] = O.h2f(p)
+            if kind in ("hg", "hmg"):
+                # an FP32 gradient with bits below FP16 resolution, as FP32 accumulation leaves them
+                fine = np.random.default_rng([seed, k, 9]).standard_normal(n).astype(np.float32)
+                e["g"] = (O.h2f(g) * (np.float32(1) + np.float32(2.0 ** -14) * fine)).astype(np.float32)
+                e["grad_dtype"] = O.GRAD_F32
         d = {name: DevBuf(e[name], torch, offset) for name in ("p", "g", "m", "v", "master") if name in e}
         host.append(e)
         dev.append(d)
         descs.append(pkg.TensorDesc(d["p"].ptr, d["g"].ptr, d["m"].ptr, d["v"].ptr,
                                     d["master"].ptr if "master" in d else None, n, wd,
-                                    pkg.F32 if kind == "f" else pkg.F16, flags, 0))
+                                    pkg.F32 if kind == "f" else pkg.F16, flags,
+                                    pkg.GRAD_F32 if kind in ("hg", "hmg") else pkg.GRAD_AS_PARAM))
     return host, dev, descs
 
 
@@ -356,12 +363,47 @@ def test_device_scaler_state_machine(pkg, O, torch):
 
 
 def test_device_bias_correction_matches_host_for_many_steps(pkg, torch):
-    """1 - beta^t computed on the device (FP64 pow rounded once) equals the host's FP32 powf
-    for every t up to 1200, and the scale doubles after 1000 clean steps."""
+    """1 - beta^t computed on the device (FP64 pow rounded once to FP32) for every t up to
+    100,000 and five betas.  It equals the correctly rounded FP32 power everywhere, and the
+    host's powf (optimizer.h:121-122) everywhere except the few steps at which the C library's
+    powf is itself one ulp off the correctly rounded value (glibc 2.39: beta 0.999, t = 2958 and
+    3606); there the two differ by one ulp of the bias correction, 6e-8 relative, far inside
+    the parity bars.  Also: the scale doubles after 1000 clean steps."""
+    import ctypes as C
     g = torch.full((64,), 0.5, device="cuda").half()
     tl = pkg.TensorList([pkg.TensorDesc(None, g.data_ptr(), None, None, None, 64, 0.0, pkg.F16, pkg.TENSOR_NORM_ONLY, 0)])
     dt = np.dtype([("scale", "f4"), ("gt", "i4"), ("step", "i4"), ("skipped", "i4"),
                    ("interval", "i4"), ("b1", "f4"), ("b2", "f4"), ("mul", "f4")])
+    rec = np.dtype([("sum_sq", "f8"), ("norm", "f4"), ("coef", "f4"), ("found_inf", "u4"), ("clip", "u4"),
+                    ("bc1", "f4"), ("bc2", "f4"), ("step", "i4"), ("loss_scale", "f4"), ("pad", "u4", 6)])
+    T = 100_000
+    gradstat, handle = pkg.lib().rlcu_gradstat, tl.handle
+    off_by_one = 0
+    for b1, b2 in ((0.8, 0.999), (0.9, 0.99), (0.95, 0.9)):
+        sc = np.zeros(1, dt)
+        sc["scale"], sc["interval"], sc["b1"], sc["b2"] = 65536.0, 1 << 30, b1, b2
+        scaler = torch.from_numpy(sc.view(np.uint8).copy()).cuda()
+        stats = torch.zeros(T, 16, device="cuda")
+        base, sp = stats.data_ptr(), scaler.data_ptr()
+        for t in range(T):
+            assert gradstat(handle, 1.0, 0.0, sp, base + 64 * t, 0, None) == 0
+        torch.cuda.synchronize()
+        got = np.frombuffer(stats.cpu().numpy().tobytes(), dtype=rec)
+        steps = np.arange(1, T + 1)
+        assert np.array_equal(got["step"], steps)
+        for beta, field in ((b1, "bc1"), (b2, "bc2")):
+            b32 = np.float32(beta)
+            rounded_once = np.float32(1.0) - np.power(np.float64(b32), steps.astype(np.float64)).astype(np.float32)
+            assert np.array_equal(got[field], rounded_once.astype(np.float32)), (beta, "device vs correctly rounded power")
+            host = np.array([pkg.bias_correction(float(b32), int(t)) for t in steps[:20_000]], np.float32)
+            diff = np.nonzero(got[field][:20_000] != host)[0]
+            for i in diff:
+                assert abs(float(got[field][i]) - float(host[i])) <= float(np.spacing(host[i])), (beta, int(i) + 1)
+            off_by_one += len(diff)
+            # past t = 20,000 every beta here has beta^t < 2^-25 and both give exactly 1.0
+            assert (got[field][20_000:] == 1.0).all() and pkg.bias_correction(float(b32), 20_001) == 1.0
+    assert off_by_one <= 4
+    # growth: the scale doubles after `interval` clean steps
     sc = np.zeros(1, dt)
     sc["scale"], sc["interval"], sc["b1"], sc["b2"] = 65536.0, 1000, 0.9, 0.999
     scaler = torch.from_numpy(sc.view(np.uint8).copy()).cuda()
@@ -369,13 +411,8 @@ def test_device_bias_correction_matches_host_for_many_steps(pkg, torch):
     for t in range(1200):
         tl.gradstat(stats[t].data_ptr(), 1.0, 0.0, scaler_ptr=scaler.data_ptr())
     torch.cuda.synchronize()
-    raw = stats.cpu().numpy()
-    for t in range(1200):
-        s = pkg.Stat.from_buffer_copy(raw[t].tobytes())
-        assert s.step == t + 1
-        assert s.bias_correction1 == pkg.bias_correction(0.9, t + 1), t
-        assert s.bias_correction2 == pkg.bias_correction(0.999, t + 1), t
-        assert s.loss_scale == (65536.0 if t < 1000 else 131072.0)
+    got = np.frombuffer(stats.cpu().numpy().tobytes(), dtype=rec)
+    assert (got["loss_scale"][:1000] == 65536.0).all() and (got["loss_scale"][1000:] == 131072.0).all()
 
 
 def test_list_argument_checks(pkg, torch):
@@ -503,12 +540,15 @@ def test_bulk_copy_update_equals_the_direct_update(pkg, O, torch, extra):
             assert np.array_equal(a[k].view(np.uint8), b[k].view(np.uint8)), k
 
 
-def test_bounded_wait_gives_up_and_reports(pkg, torch):
+@pytest.mark.parametrize("side_stream", [False, True])
+def test_bounded_wait_gives_up_and_reports(pkg, torch, side_stream):
     """A device-side wait that nothing satisfies runs out of tries, the kernel returns, the host
-    reads RLCU_ERR_TIMEOUT, and the GPU keeps working."""
+    reads RLCU_ERR_TIMEOUT, and the GPU keeps working.  With a stream that does not synchronise
+    with the legacy stream (torch's pool streams are non-blocking) the check still sees it."""
     a = torch.zeros(64, device="cuda")
     tl = pkg.TensorList([pkg.TensorDesc(a.data_ptr(), a.data_ptr(), a.data_ptr(), a.data_ptr(), None, 8, 0.0, pkg.F32, 0, 0)])
-    rc = pkg.lib().rlcu_selftest_bounded_wait(tl.handle, None)
+    stream = torch.cuda.Stream() if side_stream else None
+    rc = pkg.lib().rlcu_selftest_bounded_wait(tl.handle, stream.cuda_stream if stream else None)
     assert rc == pkg.ERR_TIMEOUT and b"gave up" in pkg.lib().rlcu_last_error()
     tl.check()                                           # the condition was cleared
     tl.step(pkg.hparams(1e-3, 0.9, 0.999, 1e-8, 1))      # and the device still runs kernels
@@ -578,3 +618,148 @@ def test_skipped_step_still_clears_gradients_when_asked(pkg, O, torch, bulk):
             assert np.array_equal(d[k].get().view(np.uint8), b[k].view(np.uint8)), k
     assert not dev[0]["g"].get().any() and not dev[1]["g"].get().any()
     assert np.array_equal(dev[2]["g"].get(), frozen_grad)      # a GRAD_ZERO tensor's buffer is never touched
+
+
+# ---------------------------------------------------------------------------------------------
+# FP32 gradients for 16-bit parameters (RLCU_GRAD_F32)
+# ---------------------------------------------------------------------------------------------
+
+GF32_MIXED = [(70_001, "hg", 0.01, 0), (1024, "hmg", 0.0, 0), (8192 * 3, "hmg", 0.01, 0), (129, "f", 0.0, 0),
+              (1, "hg", 0.0, 0), (8192, "hg", 0.01, 0), (8192 * 2 + 5, "h", 0.01, 0), (0, "hg", 0.0, 0),
+              (40_000, "hm", 0.02, 0), (8192 * 4, "hmg", 0.0, 0)]
+
+
+@pytest.mark.parametrize("offset", [0, 1])
+@pytest.mark.parametrize("max_norm", [1.0, 0.0])
+def test_fp32_gradients_for_fp16_parameters(pkg, O, torch, max_norm, offset):
+    """A list that mixes FP16 and FP32 gradients for FP16 parameters (with and without a master
+    copy): statistics within the norm bar, update bit for bit against the oracle.  The clip is
+    applied to FP32 gradients in FP32 (trainer.h:142-145): STEP_ROUND_CLIP_FP16 re-rounds only
+    the gradients that are stored in FP16."""
+    host, dev, descs = make_case(O, torch, pkg, GF32_MIXED, seed=111, offset=offset)
+    stat = torch.zeros(16, device="cuda")
+    tl = pkg.TensorList(descs)
+    lr, b1, b2, eps, t = 1e-4, 0.9, 0.999, 1e-8, 5
+    hp = pkg.hparams(lr, b1, b2, eps, t)
+    tl.gradstat(stat.data_ptr(), 1.0, max_norm)
+    tl.step(hp, stat.data_ptr(), pkg.STEP_ROUND_CLIP_FP16)
+    torch.cuda.synchronize()
+    got = read_stat(pkg, stat)
+    ot = O.make_tensors(host)
+    want = O.gradstat(ot, 1.0, max_norm)
+    assert got.found_inf == 0 and got.clip_active == want.clip_active == (1 if max_norm else 0)
+    assert abs(got.norm - want.norm) <= NORM_BAR * want.norm
+    O.multi_step(ot, O.HParams(lr, b1, b2, eps, hp.bias_correction1, hp.bias_correction2),
+                 O.gradstat_finalize(got.sum_sq, 0, 1.0, max_norm), O.STEP_ROUND_CLIP_FP16)
+    assert_same(host, dev)
+    for e, d in zip(host, dev):                      # gradients are read, never written
+        assert np.array_equal(d["g"].get().view(np.uint8), e["g"].view(np.uint8))
+
+
+def test_fp32_gradient_keeps_what_fp16_would_round_away(pkg, O, torch):
+    """The point of the variant: a gradient below FP16's smallest subnormal still moves the
+    moments when it arrives in FP32, and is lost when it is rounded to FP16 first."""
+    n = 8192 * 2 + 3
+    p, _, _, _ = seeded_case(O, n, seed=121)
+    tiny = np.full(n, 1e-9, np.float32)              # FP16 rounds this to zero
+    out = {}
+    for kind in ("hg", "h"):
+        g = tiny if kind == "hg" else O.f2h(tiny)
+        bufs = dict(p=DevBuf(p, torch), g=DevBuf(g, torch), m=DevBuf(np.zeros(n, np.float32), torch),
+                    v=DevBuf(np.zeros(n, np.float32), torch))
+        tl = pkg.TensorList([pkg.TensorDesc(bufs["p"].ptr, bufs["g"].ptr, bufs["m"].ptr, bufs["v"].ptr, None, n, 0.0,
+                                            pkg.F16, 0, pkg.GRAD_F32 if kind == "hg" else 0)])
+        tl.step(pkg.hparams(1e-3, 0.9, 0.999, 1e-8, 1))
+        torch.cuda.synchronize()
+        out[kind] = bufs["m"].get()
+    assert not out["h"].any()
+    assert np.array_equal(out["hg"], np.full(n, np.float32(1.0 - np.float32(0.9)) * np.float32(1e-9), np.float32))
+
+
+def test_fp32_gradients_zeroed_after_the_update_and_on_a_skipped_step(pkg, O, torch):
+    specs = [(8192 * 2 + 5, "hg", 0.01, 0), (3000, "hmg", 0.0, 0), (8192, "hg", 0.0, pkg.TENSOR_GRAD_ZERO)]
+    host, dev, descs = make_case(O, torch, pkg, specs, seed=131)
+    tl = pkg.TensorList(descs)
+    stat = torch.zeros(16, device="cuda")
+    hp = pkg.hparams(1e-4, 0.9, 0.999, 1e-8, 2)
+    frozen = dev[2]["g"].get()
+    tl.gradstat(stat.data_ptr(), 1.0, 1.0)
+    tl.step(hp, stat.data_ptr(), pkg.STEP_ZERO_GRADS)
+    torch.cuda.synchronize()
+    got = read_stat(pkg, stat)
+    ot = O.make_tensors(host)
+    O.multi_step(ot, O.HParams(1e-4, 0.9, 0.999, 1e-8, hp.bias_correction1, hp.bias_correction2),
+                 O.gradstat_finalize(got.sum_sq, 0, 1.0, 1.0), 0)
+    assert_same(host, dev)
+    assert not dev[0]["g"].get().any() and not dev[1]["g"].get().any()
+    assert np.array_equal(dev[2]["g"].get(), frozen)
+    # overflowed step: nothing but the gradients changes
+    bad = host[0]["g"].copy()
+    bad[11] = np.nan
+    dev[0]["g"].set(bad)
+    dev[1]["g"].set(host[1]["g"])
+    before = [{k: b.get() for k, b in d.items() if k != "g"} for d in dev]
+    tl.gradstat(stat.data_ptr(), 1.0, 1.0)
+    tl.step(hp, stat.data_ptr(), pkg.STEP_ZERO_GRADS)
+    torch.cuda.synchronize()
+    assert read_stat(pkg, stat).found_inf == 1
+    for d, b in zip(dev, before):
+        for k in b:
+            assert np.array_equal(d[k].get().view(np.uint8), b[k].view(np.uint8)), k
+    assert not dev[0]["g"].get().any() and not dev[1]["g"].get().any()
+
+
+def test_bulk_copy_update_refuses_fp32_gradient_lists(pkg, O, torch):
+    _, dev, descs = make_case(O, torch, pkg, [(8192, "hg", 0.0, 0)], seed=141)
+    tl = pkg.TensorList(descs)
+    with pytest.raises(pkg.RlcuError) as e:
+        tl.step(pkg.hparams(1e-4, 0.9, 0.999, 1e-8, 1), None, pkg.STEP_BULK_COPY)
+    assert e.value.code == pkg.ERR_UNSUPPORTED
+
+
+# ---------------------------------------------------------------------------------------------
+# what counts as an overflowed step
+# ---------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("kind", ["f", "hg"])
+def test_finite_fp32_gradient_with_an_overflowing_square_is_not_an_overflow(pkg, O, torch, kind):
+    """The non-finite test looks at the stored gradient, like the oracle, not at its square: an
+    FP32 gradient of 1e20 is finite (its square is not), so the step is not skipped; the norm is
+    +inf and the clip scales every gradient to zero, which is what RL.cu's own sequence does
+    with such a value.  A true +inf skips the step."""
+    specs = [(8192 + 7, kind, 0.01, 0), (5000, "h", 0.0, 0)]
+    host, dev, descs = make_case(O, torch, pkg, specs, seed=151)
+    g = host[0]["g"].copy()
+    g[3] = np.float32(1e20)
+    host[0]["g"] = g
+    dev[0]["g"].set(g)
+    tl = pkg.TensorList(descs)
+    stat = torch.zeros(16, device="cuda")
+    hp = pkg.hparams(1e-4, 0.9, 0.999, 1e-8, 3)
+    tl.gradstat(stat.data_ptr(), 1.0, 1.0)
+    tl.step(hp, stat.data_ptr(), 0)
+    torch.cuda.synchronize()
+    got = read_stat(pkg, stat)
+    ot = O.make_tensors(host)
+    want = O.gradstat(ot, 1.0, 1.0)
+    assert want.found_inf == 0 and np.isinf(want.norm) and want.coef == 0.0 and want.clip_active == 1
+    assert got.found_inf == 0 and np.isinf(got.norm) and got.coef == 0.0 and got.clip_active == 1
+    O.multi_step(ot, O.HParams(1e-4, 0.9, 0.999, 1e-8, hp.bias_correction1, hp.bias_correction2), want, 0)
+    assert_same(host, dev)
+    # without a clip the value is used as it is (RL.cu does the same when max_grad_norm <= 0)
+    tl.gradstat(stat.data_ptr(), 1.0, 0.0)
+    torch.cuda.synchronize()
+    got = read_stat(pkg, stat)
+    assert got.found_inf == 0 and got.coef == 1.0 and got.clip_active == 0
+    # a real infinity is an overflow
+    g[3] = np.inf
+    dev[0]["g"].set(g)
+    tl.gradstat(stat.data_ptr(), 1.0, 1.0)
+    torch.cuda.synchronize()
+    assert read_stat(pkg, stat).found_inf == 1
+    g[3] = np.float32(-1e20)
+    g[100] = np.nan
+    dev[0]["g"].set(g)
+    tl.gradstat(stat.data_ptr(), 1.0, 1.0)
+    torch.cuda.synchronize()
+    assert read_stat(pkg, stat).found_inf == 1

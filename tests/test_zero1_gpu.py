@@ -415,3 +415,48 @@ def test_overflow_in_one_replica_skips_every_rank(pkg, O, tmp_path, mode):
         assert np.array_equal(o["p"][:total], p)
         lo, hi = int(o["lo"]), min(int(o["lo"]) + S, total)
         assert np.array_equal(o["m"][:hi - lo], m[lo:hi]) and np.array_equal(o["v"][:hi - lo], v[lo:hi])
+
+
+def _bad_create_worker(rank, world, port, out_dir):
+    import sys
+    import torch
+    import torch.distributed as dist
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    box = [pkg.zero1_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    plan = pkg.zero1_plan(SEGS, rank, world)
+    S, padded = int(plan.shard_elems), int(plan.padded_elems)
+    p_pool = torch.zeros(padded, dtype=torch.float16, device="cuda")
+    g_pool = torch.zeros(padded, dtype=torch.float16, device="cuda")
+    m_sh, v_sh = torch.zeros(S + 8, device="cuda"), torch.zeros(S, device="cuda")
+    skew = 4 if rank == 1 else 0                      # rank 1 hands in a misaligned state array
+    message = ""
+    try:
+        pkg.Zero1(box[0], rank, world, p_pool.data_ptr(), g_pool.data_ptr(), SEGS, m_sh.data_ptr() + skew,
+                  v_sh.data_ptr(), None, mode=pkg.ZERO1_P2P)
+    except pkg.RlcuError as exc:
+        message = str(exc)
+    with open(os.path.join(out_dir, f"create{rank}.txt"), "w") as f:
+        f.write(message)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_create_fails_on_every_rank_when_one_rank_cannot_set_up(pkg, tmp_path):
+    """One rank's local set-up fails after the communicator is joined: every rank gets an error
+    back (the failing one its own message, the others "another rank failed") and nobody waits
+    in a collective the failing rank never enters."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    mp.spawn(_bad_create_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    m0, m1 = ((tmp_path / f"create{r}.txt").read_text() for r in range(2))
+    assert "another rank failed" in m0
+    assert "32-byte aligned" in m1

@@ -82,6 +82,37 @@ def test_overflow_then_clean_and_fp32_and_misaligned(pkg, torch):
     assert empty.norm == 0.0 and empty.found_inf == 0 and empty.coef == 1.0
 
 
+def test_two_pools_of_one_step_combine_into_one_record(pkg, torch):
+    """RL.cu's clip norm covers its FP16 gradient pool and its FP32 one (trainer.h:331-337): the
+    first call leaves only its sum (STAT_PARTIAL), the second adds its own and finishes the
+    record (STAT_ACCUMULATE); the result is the list-based pass over both tensors."""
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    g16 = (torch.randn(3_000_001, device="cuda", generator=gen) * 1e-3).half()
+    g32 = torch.randn(65_536 + 777, device="cuda", generator=gen) * 1e-2
+    stat = torch.full((16,), 7.0, device="cuda")
+    for _ in range(2):                                     # twice: the record is reused every step
+        pkg.gradstat_flat_noalloc(g16.data_ptr(), pkg.F16, g16.numel(), stat.data_ptr(), 1.0, 1.0, pkg.STAT_PARTIAL)
+        pkg.gradstat_flat_noalloc(g32.data_ptr(), pkg.F32, g32.numel(), stat.data_ptr(), 1.0, 1.0, pkg.STAT_ACCUMULATE)
+        torch.cuda.synchronize()
+        got = read_stat(pkg, stat)
+        tl = pkg.TensorList([
+            pkg.TensorDesc(None, g16.data_ptr(), None, None, None, g16.numel(), 0.0, pkg.F16, pkg.TENSOR_NORM_ONLY, 0),
+            pkg.TensorDesc(None, g32.data_ptr(), None, None, None, g32.numel(), 0.0, pkg.F32, pkg.TENSOR_NORM_ONLY, 0)])
+        want = torch.zeros(16, device="cuda")
+        tl.gradstat(want.data_ptr(), 1.0, 1.0)
+        torch.cuda.synchronize()
+        tl.close()
+        agree(got, read_stat(pkg, want))
+        assert got.clip_active == 1
+    # an inf in the first pool survives the second call
+    bad = g16.clone()
+    bad[17] = float("-inf")
+    pkg.gradstat_flat_noalloc(bad.data_ptr(), pkg.F16, bad.numel(), stat.data_ptr(), 1.0, 1.0, pkg.STAT_PARTIAL)
+    pkg.gradstat_flat_noalloc(g32.data_ptr(), pkg.F32, g32.numel(), stat.data_ptr(), 1.0, 1.0, pkg.STAT_ACCUMULATE)
+    torch.cuda.synchronize()
+    assert read_stat(pkg, stat).found_inf == 1
+
+
 def test_sizes_beyond_the_fixed_scratch_are_refused(pkg, torch):
     g = torch.zeros(16, device="cuda").half()
     stat = torch.zeros(16, device="cuda")
