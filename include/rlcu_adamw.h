@@ -81,9 +81,14 @@ enum {
     RLCU_STEP_ZERO_GRADS = 4u,      /* write zeros over each gradient after reading it:
                                        folds RL.cu's qwen3_gradients_zero (qwen3.cu:1109-1112)
                                        into the update                                   */
-    RLCU_STEP_BULK_COPY = 8u        /* move the update's HBM traffic with the bulk-copy engine
+    RLCU_STEP_BULK_COPY = 8u,       /* move the update's HBM traffic with the bulk-copy engine
                                        (cp.async.bulk through shared-memory stages) instead of
-                                       per-thread loads and stores; same results            */
+                                       per-thread loads and stores; same results.  Without this
+                                       flag or the next the library picks: lists that are mostly
+                                       FP16 weights with FP32 masters (28 bytes per element in
+                                       eight streams) take the bulk-copy kernel, which is about
+                                       5 % faster there; all others the direct kernel.       */
+    RLCU_STEP_DIRECT = 16u          /* force the per-thread load/store kernel                 */
 };
 
 /* flags of the statistics pass */
@@ -208,6 +213,8 @@ int rlcu_tensor_list_destroy(rlcu_tensor_list* list);
  * bounded wait inside a kernel launched on this list gave up since the last check
  * (RLCU_ERR_TIMEOUT); only the RLCU_STEP_BULK_COPY update has such waits.  Clears the
  * condition. */
+/* list == NULL checks the single-tensor entry points instead (rlcu_adamw_fp16_master takes the
+ * bulk-copy kernel for large tensors). */
 int rlcu_tensor_list_check(rlcu_tensor_list* list);
 /* Runs a one-thread kernel whose bounded wait is certain to run out (it waits on a
  * barrier nothing completes) and reports it through the same path: the expected
@@ -346,7 +353,10 @@ int rlcu_zero1_create(const void* unique_id, int rank, int world,
  * phases: bit mask for measurements, 0 = all.  NCCL mode: 1 reduce-scatter, 2
  * statistics + all-reduce, 4 update, 8 all-gather.  P2P mode: 1 fused
  * reduce-scatter + statistics, 2 all-reduce + finalize, 4 (or 8) fused update +
- * all-gather.  RLCU_STEP_ZERO_GRADS is not available in P2P mode. */
+ * all-gather.  With RLCU_STEP_ZERO_GRADS the whole local gradient pool is zero after the step
+ * (in P2P mode cleared inside the update kernel, under its NVLink traffic).
+ * RLCU_STEP_BULK_COPY moves the update's traffic, the peers' copies in P2P mode included,
+ * with the bulk-copy engine (FP16 pools only; bfloat16 pools take the direct path). */
 int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float max_norm,
                     rlcu_scaler_state* scaler, rlcu_stat* stat, uint32_t step_flags,
                     uint32_t phases, void* stream);

@@ -3,7 +3,7 @@
  * TEST INFRASTRUCTURE ONLY -- see adamw_oracle.h for the parity status and the
  * list of reference lines each function restates.
  *
- * Build: gcc -O2 -ffp-contract=off -mavx2 -mfma -fopenmp -shared -fPIC
+ * Build: gcc -O2 -ffp-contract=off -mavx2 -mfma -mf16c -fopenmp -shared -fPIC
  * (-ffp-contract=off keeps the compiler from fusing on its own; the rounding
  * models call fmaf() explicitly at the sites they contract.)
  */
@@ -13,6 +13,9 @@
 #include <string.h>
 #ifdef _OPENMP
 #include <omp.h>
+#endif
+#ifdef __F16C__
+#include <immintrin.h>
 #endif
 
 /* ------------------------------------------------------------------ */
@@ -58,6 +61,55 @@ uint16_t orc_f2h(float f) {
        a carry to 1<<10 is exactly the smallest normal. */
     uint32_t h = half_exp ? (((half_exp - 1u) << 10) + q) : q;
     return (uint16_t)(sign | h);
+}
+
+/* The loops below convert through H2F / F2H.  When the build has F16C and the CPU running
+ * it does too, these use the hardware conversion instructions (what any tuned CPU code
+ * would use, so that the timed CPU baseline is not slowed down by bit arithmetic); the
+ * bit-level functions above remain the definition, and tests/test_oracle.py checks the
+ * two against each other on every binary16 value and on a large sample of floats.
+ * orc_use_hw_half(0) forces the bit-level path. */
+static int g_hw_half = -1;
+
+int orc_hw_half_available(void) {
+#ifdef __F16C__
+    return __builtin_cpu_supports("f16c") ? 1 : 0;
+#else
+    return 0;
+#endif
+}
+
+void orc_use_hw_half(int on) { g_hw_half = (on && orc_hw_half_available()) ? 1 : 0; }
+
+static inline int hw_half(void) {
+    if (g_hw_half < 0) g_hw_half = orc_hw_half_available();
+    return g_hw_half;
+}
+
+#ifdef __F16C__
+static inline float hw_h2f(uint16_t h) { return _cvtsh_ss(h); }
+static inline uint16_t hw_f2h(float f) {
+    if (f != f) return (uint16_t)(((f32_bits(f) >> 16) & 0x8000u) | 0x7FFFu);   /* canonical NaN, as __float2half */
+    return (uint16_t)_cvtss_sh(f, _MM_FROUND_TO_NEAREST_INT | _MM_FROUND_NO_EXC);
+}
+#define H2F(h) (hw ? hw_h2f(h) : orc_h2f(h))
+#define F2H(f) (hw ? hw_f2h(f) : orc_f2h(f))
+#else
+#define H2F(h) orc_h2f(h)
+#define F2H(f) orc_f2h(f)
+#endif
+
+uint16_t orc_f2h_hw(float f) {
+#ifdef __F16C__
+    if (orc_hw_half_available()) return hw_f2h(f);
+#endif
+    return orc_f2h(f);
+}
+float orc_h2f_hw(uint16_t h) {
+#ifdef __F16C__
+    if (orc_hw_half_available()) return hw_h2f(h);
+#endif
+    return orc_h2f(h);
 }
 
 void orc_f2h_array(const float* src, uint16_t* dst, int64_t n) {
@@ -136,11 +188,12 @@ void orc_adamw_fp16_master(float* master_w, uint16_t* model_w, const uint16_t* g
     if (n <= 0) return;                            /* adamw.cu:49 */
     orc_k k = make_k(lr, beta1, beta2, eps, weight_decay, bc1, bc2);
     int nt = pick_threads(threads);
+    const int hw = hw_half(); (void)hw;
     #pragma omp parallel for num_threads(nt) schedule(static)
     for (int64_t i = 0; i < n; i++) {
-        float w = upd(master_w[i], orc_h2f(grad[i]), &m[i], &v[i], &k, rounding);
+        float w = upd(master_w[i], H2F(grad[i]), &m[i], &v[i], &k, rounding);
         master_w[i] = w;
-        model_w[i] = orc_f2h(w);
+        model_w[i] = F2H(w);
     }
 }
 
@@ -150,10 +203,11 @@ void orc_adamw_fp16(uint16_t* param, const uint16_t* grad, float* m, float* v, i
     if (n <= 0) return;
     orc_k k = make_k(lr, beta1, beta2, eps, weight_decay, bc1, bc2);
     int nt = pick_threads(threads);
+    const int hw = hw_half(); (void)hw;
     #pragma omp parallel for num_threads(nt) schedule(static)
     for (int64_t i = 0; i < n; i++) {
-        float w = upd(orc_h2f(param[i]), orc_h2f(grad[i]), &m[i], &v[i], &k, rounding);
-        param[i] = orc_f2h(w);
+        float w = upd(H2F(param[i]), H2F(grad[i]), &m[i], &v[i], &k, rounding);
+        param[i] = F2H(w);
     }
 }
 
@@ -175,9 +229,10 @@ void orc_adamw_fp32(float* w, const float* grad, float* m, float* v, int64_t n,
 double orc_sum_sq_half(const uint16_t* g, int64_t n, float unscale, int threads) {
     double s = 0.0;
     int nt = pick_threads(threads);
+    const int hw = hw_half(); (void)hw;
     #pragma omp parallel for num_threads(nt) schedule(static) reduction(+:s)
     for (int64_t i = 0; i < n; i++) {
-        float raw = orc_h2f(g[i]);
+        float raw = H2F(g[i]);
         float x = raw * unscale;                   /* trainer.h:108-109, FP32 product */
         float sq = x * x;
         if (isfinite(raw)) s += (double)sq;        /* inf/NaN elements are reported through found_inf */
@@ -224,8 +279,9 @@ int64_t orc_count_nonfinite_float(const float* g, int64_t n) {
 
 void orc_scale_half(uint16_t* g, int64_t n, float scale, int threads) {
     int nt = pick_threads(threads);
+    const int hw = hw_half(); (void)hw;
     #pragma omp parallel for num_threads(nt) schedule(static)
-    for (int64_t i = 0; i < n; i++) g[i] = orc_f2h(orc_h2f(g[i]) * scale);   /* trainer.h:138 */
+    for (int64_t i = 0; i < n; i++) g[i] = F2H(H2F(g[i]) * scale);   /* trainer.h:138 */
 }
 
 void orc_scale_float(float* g, int64_t n, float scale, int threads) {
@@ -311,6 +367,7 @@ int orc_multi_step(const orc_tensor* t, uint64_t count, const orc_hparams* hp,
         int zero = (d->flags & ORC_FLAG_GRAD_ZERO) != 0;
         int64_t n = (int64_t)d->n;
         if (d->dtype == ORC_F16 || d->dtype == ORC_BF16) {
+            const int hw = hw_half(); (void)hw;
             const int bf = d->dtype == ORC_BF16;
             const int gf32 = d->grad_dtype == ORC_GRAD_F32;
             uint16_t* p = (uint16_t*)d->param;
@@ -322,13 +379,13 @@ int orc_multi_step(const orc_tensor* t, uint64_t count, const orc_hparams* hp,
                 if (gf32) {
                     x = zero ? 0.0f : gf[i] * coef;                                   /* trainer.h:144 */
                 } else {
-                    x = zero ? 0.0f : (bf ? orc_bf2f(g[i]) : orc_h2f(g[i])) * coef;
-                    if (round_clip) x = bf ? orc_bf2f(orc_f2bf(x)) : orc_h2f(orc_f2h(x));   /* trainer.h:138 */
+                    x = zero ? 0.0f : (bf ? orc_bf2f(g[i]) : H2F(g[i])) * coef;
+                    if (round_clip) x = bf ? orc_bf2f(orc_f2bf(x)) : H2F(F2H(x));   /* trainer.h:138 */
                 }
-                float w0 = d->master ? d->master[i] : (bf ? orc_bf2f(p[i]) : orc_h2f(p[i]));
+                float w0 = d->master ? d->master[i] : (bf ? orc_bf2f(p[i]) : H2F(p[i]));
                 float w = upd(w0, x, &d->m[i], &d->v[i], &kk, rounding);
                 if (d->master) d->master[i] = w;
-                p[i] = bf ? orc_f2bf(w) : orc_f2h(w);
+                p[i] = bf ? orc_f2bf(w) : F2H(w);
             }
         } else {
             float* p = (float*)d->param;

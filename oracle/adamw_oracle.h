@@ -98,6 +98,13 @@ uint16_t orc_f2h(float f);
 float    orc_h2f(uint16_t h);
 void     orc_f2h_array(const float* src, uint16_t* dst, int64_t n);
 void     orc_h2f_array(const uint16_t* src, float* dst, int64_t n);
+/* The same two conversions through the CPU's F16C instructions when the build and the CPU
+ * have them (else they fall back to the functions above).  The update and norm loops use
+ * these by default; orc_use_hw_half(0) switches them to the bit-level definition. */
+uint16_t orc_f2h_hw(float f);
+float    orc_h2f_hw(uint16_t h);
+int      orc_hw_half_available(void);
+void     orc_use_hw_half(int on);
 /* bfloat16 <-> binary32, round-to-nearest-even (NaN kept quiet) */
 uint16_t orc_f2bf(float f);
 float    orc_bf2f(uint16_t b);

@@ -74,6 +74,10 @@ def lib() -> C.CDLL:
         hyper = [f] * 7
         L.orc_f2h.argtypes, L.orc_f2h.restype = [f], C.c_uint16
         L.orc_h2f.argtypes, L.orc_h2f.restype = [C.c_uint16], f
+        L.orc_f2h_hw.argtypes, L.orc_f2h_hw.restype = [f], C.c_uint16
+        L.orc_h2f_hw.argtypes, L.orc_h2f_hw.restype = [C.c_uint16], f
+        L.orc_hw_half_available.restype = i32
+        L.orc_use_hw_half.argtypes = [i32]
         L.orc_f2h_array.argtypes = [vp, vp, i64]
         L.orc_h2f_array.argtypes = [vp, vp, i64]
         L.orc_f2bf_array.argtypes = [vp, vp, i64]
@@ -132,6 +136,15 @@ def bf2f(b: np.ndarray) -> np.ndarray:
     out = np.empty(b.shape, dtype=np.float32)
     lib().orc_bf2f_array(_p(b), _p(out), b.size)
     return out
+
+
+def hw_half_available() -> bool:
+    """Whether the timed loops convert halves with the CPU's F16C instructions."""
+    return bool(lib().orc_hw_half_available())
+
+
+def use_hw_half(on: bool) -> None:
+    lib().orc_use_hw_half(1 if on else 0)
 
 
 def bias_correction(beta: float, step: int) -> float:

@@ -24,7 +24,7 @@ OK, ERR_INVALID, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_UNSUPPORTED = range(6)
 F16, F32, BF16 = 0, 1, 2
 GRAD_AS_PARAM, GRAD_F32 = 0, 1
 TENSOR_NORM_ONLY, TENSOR_GRAD_ZERO = 1, 2
-STEP_ROUND_CLIP_FP16, STEP_DEVICE_BIAS_CORRECTION, STEP_ZERO_GRADS, STEP_BULK_COPY = 1, 2, 4, 8
+STEP_ROUND_CLIP_FP16, STEP_DEVICE_BIAS_CORRECTION, STEP_ZERO_GRADS, STEP_BULK_COPY, STEP_DIRECT = 1, 2, 4, 8, 16
 STAT_PARTIAL, STAT_ACCUMULATE = 1, 2
 
 # every symbol include/rlcu_adamw.h declares

@@ -97,7 +97,9 @@ __device__ __forceinline__ void bulk_issue_tile(const WorkItem& it, int sub, uns
 }
 
 // Issues the stores of one finished tile (one thread) and commits them as one group.
-__device__ __forceinline__ void bulk_store_tile(const WorkItem& it, int sub, unsigned char* stage, bool zero_grads) {
+template <bool PEERS>
+__device__ __forceinline__ void bulk_store_tile(const WorkItem& it, int sub, unsigned char* stage, bool zero_grads,
+                                                const PeerOut& peers) {
     const size_t e = (size_t)sub * kBulkTile;
     const bool master = (it.flags & kItemKindMask) == kItemKindF16Master;
     const uint32_t s = smem_u32(stage);
@@ -105,6 +107,11 @@ __device__ __forceinline__ void bulk_store_tile(const WorkItem& it, int sub, uns
     bulk_store(it.v + e, s + 8192, kBulkTile * 4);
     if (master) bulk_store(it.master + e, s + 16384, kBulkTile * 4);
     bulk_store(static_cast<__half*>(it.p) + e, s + 24576, kBulkTile * 2);
+    if constexpr (PEERS) {
+        // the same 4 KB of new parameters into every peer's pool, over NVLink
+        const ptrdiff_t off = (static_cast<__half*>(it.p) + e) - peers.local_base;
+        for (int j = 0; j < peers.n; j++) bulk_store(peers.base[j] + off, s + 24576, kBulkTile * 2);
+    }
     if (zero_grads && !(it.flags & RLCU_TENSOR_GRAD_ZERO))
         bulk_store(const_cast<__half*>(static_cast<const __half*>(it.g)) + e, s + 28672, kBulkTile * 2);
     bulk_commit();
@@ -157,6 +164,134 @@ __device__ __forceinline__ void bulk_compute_tile(const WorkItem& it, unsigned c
     out.y = *reinterpret_cast<uint32_t*>(&hi);
     *sp = out;
     if (xf.zero_grads && !zero) *sg = make_uint2(0u, 0u);
+}
+
+// Body of the bulk-copy update kernels (launch: kBulkThreads + 32 threads, one CTA per SM,
+// kBulkSmemBytes of dynamic shared memory): kBulkThreads consumer threads do the arithmetic
+// in shared memory while one thread of the extra warp drives cp.async.bulk loads and stores
+// through a ring of kBulkStages stages.  Producer and consumers meet only at the stages'
+// full/empty barriers.  With PEERS every finished tile of FP16 parameters is also stored,
+// by the same engine, at the same offset of each peer GPU's parameter pool (the all-gather
+// of the sharded step); a skipped step then stores nothing anywhere.
+// Where the work items come from: a table in device memory (tensor lists), or one tensor
+// cut into kChunk-element items on the fly (the single-tensor entry points).
+using TableItems = TableRef;
+struct FlatItems {
+    WorkItem base;      // pointers at the tensor's first element; flags carry kind and alignment
+    uint64_t n;         // elements in the tensor
+    __device__ __forceinline__ WorkItem get(uint32_t idx) const {
+        const uint64_t off = (uint64_t)idx * kChunk;
+        WorkItem it = base;
+        it.count = (uint32_t)((n - off) < (uint64_t)kChunk ? (n - off) : (uint64_t)kChunk);
+        it.m += off;
+        it.v += off;
+        if (it.master) it.master += off;
+        const size_t esz = (base.flags & kItemKindMask) == kItemKindF32 ? 4 : 2;
+        it.p = static_cast<char*>(base.p) + off * esz;
+        it.g = static_cast<const char*>(base.g) + off * esz;
+        return it;
+    }
+};
+
+template <bool PEERS, class Items>
+__device__ __forceinline__ void bulk_table_body(const Items items, uint32_t n_items, StepConsts c,
+                                                const rlcu_stat* __restrict__ stat, uint32_t step_flags,
+                                                unsigned int* error_word, const PeerOut& peers) {
+    extern __shared__ __align__(128) unsigned char ring[];
+    __shared__ __align__(8) unsigned long long full_bar[kBulkStages];
+    __shared__ __align__(8) unsigned long long empty_bar[kBulkStages];
+    GradXform xf;
+    if (!resolve_step(stat, step_flags, c, xf)) {
+        if (!(step_flags & RLCU_STEP_ZERO_GRADS)) return;
+        clear_gradients(items, n_items);
+        return;
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kBulkStages; s++) {
+            mbar_init(smem_u32(&full_bar[s]), 1);                    // the producer's expect_tx
+            mbar_init(smem_u32(&empty_bar[s]), kBulkThreads / 32);   // one arrival per consumer warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (threadIdx.x >= kBulkThreads) {
+        // ---------------- producer warp: one thread issues every bulk copy ----------------
+        if (threadIdx.x != kBulkThreads) return;
+        uint32_t load_item_idx = blockIdx.x, loaded = 0;     // next tile to load
+        uint32_t store_item_idx = blockIdx.x, stored = 0;    // next tile to store
+        int load_sub = 0, store_sub = 0;
+        WorkItem lit, sit;
+        bool have_l = false, have_s = false, bail = false;
+        auto next_eligible = [&](uint32_t& idx, WorkItem& it, bool& have) {
+            while (!have && idx < n_items) {
+                it = items.get(idx);
+                if (bulk_eligible(it)) have = true;
+                else idx += gridDim.x;
+            }
+            return have;
+        };
+        auto load_upto = [&](uint32_t upto) {
+            while (loaded < upto && next_eligible(load_item_idx, lit, have_l)) {
+                const int stage = loaded % kBulkStages;
+                bulk_issue_tile(lit, load_sub, ring + (size_t)stage * kBulkStageBytes, smem_u32(&full_bar[stage]));
+                loaded++;
+                if (++load_sub == kBulkTilesPerItem) {
+                    load_sub = 0;
+                    load_item_idx += gridDim.x;
+                    have_l = false;
+                }
+            }
+        };
+        load_upto(kBulkDepth);
+        while (next_eligible(store_item_idx, sit, have_s)) {
+            const int stage = stored % kBulkStages;
+            // the consumers have finished tile `stored` in this stage
+            if (!mbar_wait(smem_u32(&empty_bar[stage]), (stored / kBulkStages) & 1u)) {
+                bail = true;
+                break;
+            }
+            bulk_store_tile<PEERS>(sit, store_sub, ring + (size_t)stage * kBulkStageBytes, xf.zero_grads, peers);
+            stored++;
+            if (++store_sub == kBulkTilesPerItem) {
+                store_sub = 0;
+                store_item_idx += gridDim.x;
+                have_s = false;
+            }
+            bulk_wait_read<1>();                 // the stage refilled next was stored two tiles ago
+            load_upto(stored + kBulkDepth);
+        }
+        if (bail) {
+            atomicExch(error_word, 1u);
+            // loads already issued still land in this CTA's shared memory: wait for them (bounded)
+            for (uint32_t t = stored; t < loaded; t++)
+                mbar_wait(smem_u32(&full_bar[t % kBulkStages]), (t / kBulkStages) & 1u);
+        }
+        bulk_wait_all();
+        return;
+    }
+
+    // ---------------- consumer warps ----------------
+    uint32_t tiles = 0;
+    for (uint32_t idx = blockIdx.x; idx < n_items; idx += gridDim.x) {
+        const WorkItem it = items.get(idx);
+        if (!bulk_eligible(it)) {
+            if (threadIdx.x < kThreads) process_item<PEERS>(it, c, xf, peers);
+            continue;
+        }
+        for (int sub = 0; sub < kBulkTilesPerItem; sub++) {
+            const int stage = tiles % kBulkStages;
+            if (!mbar_wait(smem_u32(&full_bar[stage]), (tiles / kBulkStages) & 1u)) {
+                atomicExch(error_word, 1u);      // stop arriving: the producer's wait runs out too
+                return;
+            }
+            bulk_compute_tile(it, ring + (size_t)stage * kBulkStageBytes, c, xf);
+            fence_async_smem();                  // results visible to the bulk store
+            __syncwarp();
+            if ((threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
+            tiles++;
+        }
+    }
 }
 
 }  // namespace rlcu

@@ -265,11 +265,18 @@ __device__ __forceinline__ WorkItem load_item(const WorkItem* table, uint32_t id
     return it;
 }
 
+struct TableRef {     // a work table in device memory
+    const WorkItem* table;
+    __device__ __forceinline__ WorkItem get(uint32_t idx) const { return load_item(table, idx); }
+};
+__device__ __forceinline__ void clear_gradients(const WorkItem* table, uint32_t n_items);
+
 // What a skipped (overflowed) step still does when RLCU_STEP_ZERO_GRADS is set: the stale
 // gradients are cleared, parameters and moments stay untouched.
-__device__ __forceinline__ void clear_gradients(const WorkItem* table, uint32_t n_items) {
+template <class Items>
+__device__ __forceinline__ void clear_gradients(const Items& items, uint32_t n_items) {
     for (uint32_t idx = blockIdx.x; idx < n_items; idx += gridDim.x) {
-        const WorkItem it = load_item(table, idx);
+        const WorkItem it = items.get(idx);
         if (it.flags & (RLCU_TENSOR_NORM_ONLY | RLCU_TENSOR_GRAD_ZERO)) continue;
         const bool f32 = (it.flags & kItemKindMask) == kItemKindF32 || (it.flags & kItemGradF32);
         const uint32_t per_vec = f32 ? 4u : 8u;          // elements in 16 bytes
@@ -288,6 +295,10 @@ __device__ __forceinline__ void clear_gradients(const WorkItem* table, uint32_t 
             for (uint32_t i = done + threadIdx.x; i < it.count; i += blockDim.x) g[i] = __float2half_rn(0.0f);
         }
     }
+}
+
+__device__ __forceinline__ void clear_gradients(const WorkItem* table, uint32_t n_items) {
+    clear_gradients(TableRef{table}, n_items);
 }
 
 // Resolves the per-launch constants from the statistics record (if any).

@@ -22,6 +22,7 @@
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -72,108 +73,26 @@ adamw_table_kernel(const WorkItem* __restrict__ table, uint32_t n_items, StepCon
 
 // Multi-tensor update, bulk-copy variant: one CTA per SM; kBulkThreads consumer threads do
 // the arithmetic in shared memory while one thread of an extra warp drives cp.async.bulk
-// loads and stores through a ring of kBulkStages stages (see adamw_bulk.cuh).  Producer and
-// consumers meet only at the stages' full/empty barriers.
+// loads and stores through a ring of kBulkStages stages (bulk_table_body in adamw_bulk.cuh).
 __global__ void __launch_bounds__(kBulkThreads + 32, 1)
 adamw_table_bulk_kernel(const WorkItem* __restrict__ table, uint32_t n_items, StepConsts c,
                         const rlcu_stat* __restrict__ stat, uint32_t step_flags,
                         unsigned int* error_word) {
-    extern __shared__ __align__(128) unsigned char ring[];
-    __shared__ __align__(8) unsigned long long full_bar[kBulkStages];
-    __shared__ __align__(8) unsigned long long empty_bar[kBulkStages];
-    GradXform xf;
-    if (!resolve_step(stat, step_flags, c, xf)) {
-        if (!(step_flags & RLCU_STEP_ZERO_GRADS)) return;
-        clear_gradients(table, n_items);
-        return;
-    }
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kBulkStages; s++) {
-            mbar_init(smem_u32(&full_bar[s]), 1);                    // the producer's expect_tx
-            mbar_init(smem_u32(&empty_bar[s]), kBulkThreads / 32);   // one arrival per consumer warp
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-
-    if (threadIdx.x >= kBulkThreads) {
-        // ---------------- producer warp: one thread issues every bulk copy ----------------
-        if (threadIdx.x != kBulkThreads) return;
-        uint32_t load_item_idx = blockIdx.x, loaded = 0;     // next tile to load
-        uint32_t store_item_idx = blockIdx.x, stored = 0;    // next tile to store
-        int load_sub = 0, store_sub = 0;
-        WorkItem lit, sit;
-        bool have_l = false, have_s = false, bail = false;
-        auto next_eligible = [&](uint32_t& idx, WorkItem& it, bool& have) {
-            while (!have && idx < n_items) {
-                it = load_item(table, idx);
-                if (bulk_eligible(it)) have = true;
-                else idx += gridDim.x;
-            }
-            return have;
-        };
-        auto load_upto = [&](uint32_t upto) {
-            while (loaded < upto && next_eligible(load_item_idx, lit, have_l)) {
-                const int stage = loaded % kBulkStages;
-                bulk_issue_tile(lit, load_sub, ring + (size_t)stage * kBulkStageBytes, smem_u32(&full_bar[stage]));
-                loaded++;
-                if (++load_sub == kBulkTilesPerItem) {
-                    load_sub = 0;
-                    load_item_idx += gridDim.x;
-                    have_l = false;
-                }
-            }
-        };
-        load_upto(kBulkDepth);
-        while (next_eligible(store_item_idx, sit, have_s)) {
-            const int stage = stored % kBulkStages;
-            // the consumers have finished tile `stored` in this stage
-            if (!mbar_wait(smem_u32(&empty_bar[stage]), (stored / kBulkStages) & 1u)) {
-                bail = true;
-                break;
-            }
-            bulk_store_tile(sit, store_sub, ring + (size_t)stage * kBulkStageBytes, xf.zero_grads);
-            stored++;
-            if (++store_sub == kBulkTilesPerItem) {
-                store_sub = 0;
-                store_item_idx += gridDim.x;
-                have_s = false;
-            }
-            bulk_wait_read<1>();                 // the stage refilled next was stored two tiles ago
-            load_upto(stored + kBulkDepth);
-        }
-        if (bail) {
-            atomicExch(error_word, 1u);
-            // loads already issued still land in this CTA's shared memory: wait for them (bounded)
-            for (uint32_t t = stored; t < loaded; t++)
-                mbar_wait(smem_u32(&full_bar[t % kBulkStages]), (t / kBulkStages) & 1u);
-        }
-        bulk_wait_all();
-        return;
-    }
-
-    // ---------------- consumer warps ----------------
-    uint32_t tiles = 0;
-    for (uint32_t idx = blockIdx.x; idx < n_items; idx += gridDim.x) {
-        const WorkItem it = load_item(table, idx);
-        if (!bulk_eligible(it)) {
-            if (threadIdx.x < kThreads) process_item<false>(it, c, xf, PeerOut{});
-            continue;
-        }
-        for (int sub = 0; sub < kBulkTilesPerItem; sub++) {
-            const int stage = tiles % kBulkStages;
-            if (!mbar_wait(smem_u32(&full_bar[stage]), (tiles / kBulkStages) & 1u)) {
-                atomicExch(error_word, 1u);      // stop arriving: the producer's wait runs out too
-                return;
-            }
-            bulk_compute_tile(it, ring + (size_t)stage * kBulkStageBytes, c, xf);
-            fence_async_smem();                  // results visible to the bulk store
-            __syncwarp();
-            if ((threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
-            tiles++;
-        }
-    }
+    bulk_table_body<false>(TableItems{table}, n_items, c, stat, step_flags, error_word, PeerOut{});
 }
+
+// The same for one tensor (RL.cu's launch_adamw_fp16 shape): items are cut on the fly.
+__global__ void __launch_bounds__(kBulkThreads + 32, 1)
+adamw_flat_bulk_kernel(const __grid_constant__ FlatItems items, uint32_t n_items, StepConsts c,
+                       unsigned int* error_word) {
+    bulk_table_body<false>(items, n_items, c, nullptr, 0u, error_word, PeerOut{});
+}
+
+// Error word of the launches that have no tensor list to keep one in (the single-tensor entry
+// points): set when a bounded wait of adamw_flat_bulk_kernel gives up, read and cleared by
+// rlcu_tensor_list_check(NULL).  In host code this name is only a handle for
+// cudaGetSymbolAddress.
+static __device__ unsigned int flat_error_word;
 
 // Exercises the give-up path of the bounded barrier wait: waits on a barrier that
 // nothing will ever complete, with a small try budget, and records the outcome the way
@@ -428,6 +347,7 @@ using namespace rlcu;
 namespace {
 
 struct DeviceInfo {
+    unsigned int* flat_error = nullptr;   // device address of flat_error_word
     int sms = 0;
     int occ_table = 0, occ_table_gf32 = 0, occ_flat = 0, occ_stat = 0;
 };
@@ -451,6 +371,11 @@ int device_info(DeviceInfo* out) {
         // the bulk-copy variant needs its 192 KB ring opted in once per device
         RLCU_CUDA(cudaFuncSetAttribute(adamw_table_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kBulkSmemBytes));
+        RLCU_CUDA(cudaFuncSetAttribute(adamw_flat_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kBulkSmemBytes));
+        void* word = nullptr;
+        RLCU_CUDA(cudaGetSymbolAddress(&word, flat_error_word));
+        di.flat_error = static_cast<unsigned int*>(word);
         if (di.occ_table < 1 || di.occ_table_gf32 < 1 || di.occ_flat < 1 || di.occ_stat < 1)
             return set_error(RLCU_ERR_CUDA, "kernel does not fit on an SM");
         cache[dev] = di;
@@ -458,6 +383,16 @@ int device_info(DeviceInfo* out) {
     }
     *out = cache[dev];
     return RLCU_OK;
+}
+
+// RLCU_DIRECT_ONLY=1 in the environment keeps every launch on the per-thread load/store
+// kernels (for measurements, and as a switch should the bulk-copy engine misbehave).
+bool direct_only() {
+    static const bool on = [] {
+        const char* e = getenv("RLCU_DIRECT_ONLY");
+        return e && e[0] && e[0] != '0';
+    }();
+    return on;
 }
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
@@ -548,6 +483,21 @@ int launch_flat(const rlcu_tensor_desc& d, int64_t n, float lr, float b1, float 
     // 32-byte alignment the tensor's first element has
     base.flags = bits | item_alignment(base, d);
     const uint64_t items = ((uint64_t)n + kChunk - 1) / kChunk;
+    // FP16 weights with an FP32 master copy (what RL.cu's launch_adamw_fp16 is) move 28 bytes per
+    // element in eight streams; issued as 4-8 KB bulk copies they reach 0.98 of the measured
+    // HBM bandwidth where per-thread accesses reach 0.93, so large tensors of that kind take
+    // the bulk-copy kernel.  Small ones, and every other kind, take the direct kernel.
+    const bool bulk = d.master && d.dtype == RLCU_F16 && (base.flags & kItemVec16) &&
+                      items >= 4ull * (uint64_t)di.sms && items <= 0xFFFFFFFFull && !direct_only();
+    if (bulk) {
+        FlatItems fi;
+        fi.base = base;
+        fi.n = (uint64_t)n;
+        adamw_flat_bulk_kernel<<<di.sms, kBulkThreads + 32, kBulkSmemBytes, (cudaStream_t)stream>>>(
+            fi, (uint32_t)items, make_consts(lr, b1, b2, eps, bc1, bc2), di.flat_error);
+        RLCU_CUDA(cudaGetLastError());
+        return RLCU_OK;
+    }
     const uint64_t cap = (uint64_t)di.sms * di.occ_flat;
     const int grid = (int)(items < cap ? items : cap);
     adamw_flat_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>(
@@ -634,7 +584,7 @@ int rlcu_tensor_list_create(const rlcu_tensor_desc* descs, uint64_t count, rlcu_
     if (rc) return rc;
 
     std::vector<WorkItem> items;
-    uint64_t numel = 0, stat_numel = 0;
+    uint64_t numel = 0, stat_numel = 0, master_numel = 0;
     bool any_grad_f32 = false;
     for (uint64_t k = 0; k < count; k++) {
         const rlcu_tensor_desc& d = descs[k];
@@ -649,6 +599,7 @@ int rlcu_tensor_list_create(const rlcu_tensor_desc* descs, uint64_t count, rlcu_
         const size_t esz = d.dtype == RLCU_F32 ? 4 : 2;
         const size_t gesz = grad_elem_size(d);
         if (bits & kItemGradF32) any_grad_f32 = true;
+        if (!(d.flags & RLCU_TENSOR_NORM_ONLY) && d.master && d.dtype == RLCU_F16 && !(bits & kItemGradF32)) master_numel += d.n;
         // Work items are cut so that, from the second one on, every pointer sits on a
         // 128-byte line: a tensor that starts in the middle of a line (ragged sizes packed
         // into one arena) gets a short head item first.  Without this a warp's accesses
@@ -680,6 +631,9 @@ int rlcu_tensor_list_create(const rlcu_tensor_desc* descs, uint64_t count, rlcu_
     L->numel = numel;
     L->stat_numel = stat_numel;
     L->has_grad_f32 = any_grad_f32;
+    // lists that are mostly FP16 weights with FP32 masters run faster through the bulk-copy
+    // kernel (see launch_flat); the others through the direct one
+    L->prefer_bulk = !any_grad_f32 && master_numel * 2 > numel && items.size() >= 4ull * (uint64_t)di.sms;
     const uint64_t cap_u = (uint64_t)di.sms * (any_grad_f32 ? di.occ_table_gf32 : di.occ_table), cap_s = (uint64_t)di.sms * di.occ_stat;
     L->grid_update = (int)(L->n_items < cap_u ? (L->n_items ? L->n_items : 1) : cap_u);
     L->grid_stat = (int)(L->n_items < cap_s ? (L->n_items ? L->n_items : 1) : cap_s);
@@ -718,8 +672,20 @@ int rlcu_tensor_list_destroy(rlcu_tensor_list* list) {
 }
 
 int rlcu_tensor_list_check(rlcu_tensor_list* list) {
-    if (!list) return set_error(RLCU_ERR_INVALID, "null list");
     unsigned int word = 0;
+    if (!list) {
+        // the single-tensor entry points keep their error word in the library image
+        DeviceInfo di;
+        const int rc = device_info(&di);
+        if (rc) return rc;
+        RLCU_CUDA(cudaDeviceSynchronize());
+        RLCU_CUDA(cudaMemcpy(&word, di.flat_error, sizeof(word), cudaMemcpyDeviceToHost));
+        if (word) {
+            cudaMemset(di.flat_error, 0, sizeof(word));
+            return set_error(RLCU_ERR_TIMEOUT, "a bulk-copy wait in a single-tensor update gave up; that update is incomplete");
+        }
+        return RLCU_OK;
+    }
     // A blocking copy on the legacy stream does not wait for streams created with
     // cudaStreamNonBlocking, so wait for the whole device first.
     RLCU_CUDA(cudaDeviceSynchronize());
@@ -747,6 +713,7 @@ int rlcu_gradstat(rlcu_tensor_list* list, float unscale, float max_norm,
     if (!list || !stat_out) return set_error(RLCU_ERR_INVALID, "null list or stat");
     if (flags & ~(uint32_t)RLCU_STAT_PARTIAL) return set_error(RLCU_ERR_INVALID, "unknown flags");
     if (!aligned(stat_out, 16)) return set_error(RLCU_ERR_INVALID, "stat record must be 16-byte aligned");
+    NvtxRange range("rlcu: gradient statistics");
     gradstat_kernel<<<list->grid_stat, kThreads, 0, (cudaStream_t)stream>>>(
         list->d_items, list->n_items, unscale, max_norm, scaler, stat_out, flags,
         list->d_partials, list->d_counter);
@@ -766,11 +733,16 @@ int rlcu_adamw_multi_step(rlcu_tensor_list* list, const rlcu_hparams* hp,
                           const rlcu_stat* stat, uint32_t step_flags, void* stream) {
     if (!list || !hp) return set_error(RLCU_ERR_INVALID, "null list or hparams");
     const uint32_t known = RLCU_STEP_ROUND_CLIP_FP16 | RLCU_STEP_DEVICE_BIAS_CORRECTION | RLCU_STEP_ZERO_GRADS |
-                           RLCU_STEP_BULK_COPY;
+                           RLCU_STEP_BULK_COPY | RLCU_STEP_DIRECT;
     if (step_flags & ~known) return set_error(RLCU_ERR_INVALID, "unknown step flags");
     if ((step_flags & RLCU_STEP_DEVICE_BIAS_CORRECTION) && !stat)
         return set_error(RLCU_ERR_INVALID, "device bias correction needs a statistics record");
     if (list->n_items == 0) return RLCU_OK;
+    NvtxRange range("rlcu: AdamW update");
+    if ((step_flags & RLCU_STEP_BULK_COPY) && (step_flags & RLCU_STEP_DIRECT))
+        return set_error(RLCU_ERR_INVALID, "RLCU_STEP_BULK_COPY and RLCU_STEP_DIRECT exclude each other");
+    if (!(step_flags & RLCU_STEP_DIRECT) && list->prefer_bulk && !direct_only()) step_flags |= RLCU_STEP_BULK_COPY;
+    step_flags &= ~(uint32_t)RLCU_STEP_DIRECT;
     if (step_flags & RLCU_STEP_BULK_COPY) {
         if (list->has_grad_f32)
             return set_error(RLCU_ERR_UNSUPPORTED, "the bulk-copy update does not take FP32 gradients for 16-bit parameters");

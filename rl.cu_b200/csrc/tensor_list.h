@@ -10,6 +10,7 @@ struct rlcu_tensor_list {
     uint32_t n_items = 0;
     uint64_t numel = 0;        // elements the update pass touches
     uint64_t stat_numel = 0;   // elements the statistics pass reads
+    bool prefer_bulk = false;  // mostly FP16 weights with FP32 masters: the bulk-copy kernel is the faster one
     bool has_grad_f32 = false; // some 16-bit parameter has FP32 gradients (selects the kernel instantiation)
     float* d_partials = nullptr;
     unsigned int* d_counter = nullptr;

@@ -417,29 +417,40 @@ int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float 
     // ones to the division); 1/world goes into the factor applied in registers
     const float unscale_all = unscale / (float)z->world;
     int rc;
-    const uint32_t known_flags = RLCU_STEP_ROUND_CLIP_FP16 | RLCU_STEP_DEVICE_BIAS_CORRECTION | RLCU_STEP_ZERO_GRADS;
+    const uint32_t known_flags = RLCU_STEP_ROUND_CLIP_FP16 | RLCU_STEP_DEVICE_BIAS_CORRECTION | RLCU_STEP_ZERO_GRADS |
+                                 RLCU_STEP_BULK_COPY | RLCU_STEP_DIRECT;
     if (step_flags & ~known_flags)
         return set_error(RLCU_ERR_INVALID, "step flags 0x%x are not available in the sharded step", step_flags & ~known_flags);
     if ((step_flags & RLCU_STEP_DEVICE_BIAS_CORRECTION) && !scaler)
         return set_error(RLCU_ERR_INVALID, "device bias correction needs a scaler state");
+    // RLCU_STEP_ZERO_GRADS clears the WHOLE local gradient pool: the shard inside the update
+    // kernel (each gradient after it was read), the rest beside it.
+    const uint64_t total_bytes = z->plan.padded_elems * 2, shard_lo = (uint64_t)z->rank * S * 2, shard_hi = shard_lo + S * 2;
+    rlcu::ZeroSpan zero{};
+    zero.a = reinterpret_cast<uint4*>(z->grad_pool);
+    zero.a_vecs = shard_lo / 16;
+    zero.b = reinterpret_cast<uint4*>(static_cast<char*>(z->grad_pool) + shard_hi);
+    zero.b_vecs = (total_bytes - shard_hi) / 16;
     if (z->mode == RLCU_ZERO1_P2P) {
-        if (step_flags & RLCU_STEP_ZERO_GRADS)
-            return set_error(RLCU_ERR_UNSUPPORTED, "RLCU_STEP_ZERO_GRADS is not available in the sharded step");
         if (phases & 1u) {
+            rlcu::NvtxRange range("rlcu zero1: reduce-scatter + statistics (peer loads)");
             // every rank's gradients are complete before anyone reads them remotely
             rc = barrier(z, s);
             if (rc) return rc;
-            rc = rlcu::launch_reduce_stat(z->list, z->grads_in, unscale_all, scaler, stat, s);
+            rc = rlcu::launch_reduce_stat(z->list, z->grads_in, unscale_all, scaler, stat,
+                                          (step_flags & RLCU_STEP_BULK_COPY) != 0, s);
             if (rc) return rc;
         }
         if (phases & 2u) {
+            rlcu::NvtxRange range("rlcu zero1: norm all-reduce + finalize");
             // the sum over ranks doubles as "all remote reads of my gradients are done"
             RLCU_NCCL(z->api, z->api->AllReduce(&stat->sum_sq, &stat->sum_sq, 1, ncclDouble, ncclSum, z->comm, s));
             rc = rlcu_gradstat_finalize(stat, unscale_all, max_norm, scaler, s);
             if (rc) return rc;
         }
         if (phases & (4u | 8u)) {
-            rc = rlcu::launch_update_peers(z->list, hp, stat, step_flags, z->params_out, s);
+            rlcu::NvtxRange range("rlcu zero1: update + all-gather (peer stores)");
+            rc = rlcu::launch_update_peers(z->list, hp, stat, step_flags, z->params_out, zero, s);
             if (rc) return rc;
             // every rank's stores into my pool have landed before I use the parameters
             rc = barrier(z, s);
@@ -447,9 +458,12 @@ int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float 
         }
         return RLCU_OK;
     }
-    if (phases & 1u)
+    if (phases & 1u) {
+        rlcu::NvtxRange range("rlcu zero1: ncclReduceScatter");
         RLCU_NCCL(z->api, z->api->ReduceScatter(z->grad_pool, gshard, S, z->wire_type, ncclSum, z->comm, s));
+    }
     if (phases & 2u) {
+        rlcu::NvtxRange range("rlcu zero1: statistics + norm all-reduce");
         rc = rlcu_gradstat(z->list, unscale_all, max_norm, scaler, stat, RLCU_STAT_PARTIAL, s);
         if (rc) return rc;
         RLCU_NCCL(z->api, z->api->AllReduce(&stat->sum_sq, &stat->sum_sq, 1, ncclDouble, ncclSum, z->comm, s));
@@ -459,9 +473,15 @@ int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float 
     if (phases & 4u) {
         rc = rlcu_adamw_multi_step(z->list, hp, stat, step_flags, s);
         if (rc) return rc;
+        if (step_flags & RLCU_STEP_ZERO_GRADS) {      // the stale partial sums outside the shard
+            if (zero.a_vecs) RLCU_CUDA(cudaMemsetAsync(zero.a, 0, zero.a_vecs * 16, s));
+            if (zero.b_vecs) RLCU_CUDA(cudaMemsetAsync(zero.b, 0, zero.b_vecs * 16, s));
+        }
     }
-    if (phases & 8u)
+    if (phases & 8u) {
+        rlcu::NvtxRange range("rlcu zero1: ncclAllGather");
         RLCU_NCCL(z->api, z->api->AllGather(pshard, z->param_pool, S, z->wire_type, z->comm, s));
+    }
     return RLCU_OK;
 }
 

@@ -16,6 +16,7 @@
 
 #include <mutex>
 
+#include "adamw_bulk.cuh"
 #include "adamw_update.cuh"
 #include "host_util.h"
 #include "tensor_list.h"
@@ -201,14 +202,235 @@ reduce_stat_kernel(const WorkItem* __restrict__ table, uint32_t n_items,
     }
 }
 
+// ---------------------------------------------------------------------------
+// reduce-scatter + statistics with the peers' gradients fetched by the bulk-copy engine
+// ---------------------------------------------------------------------------
+// Same result as reduce_stat_kernel, bit for bit in the reduced gradients (FP32 sum in rank
+// order, one rounding).  One CTA per SM: a producer thread keeps kRbDepth tiles in flight,
+// each tile being kRbTile consecutive elements fetched from every rank's pool with one
+// cp.async.bulk per rank (plain bulk loads from peer-mapped memory, no multicast), and
+// kBulkThreads consumer threads add the ranks' copies out of shared memory.  Large requests
+// from the copy engine use the links better than per-thread loads do.
+constexpr int kRbTile = 2048;                          // elements per rank per stage
+constexpr int kRbTileBytes = kRbTile * 2;
+constexpr int kRbStageBytes = kMaxWorld * kRbTileBytes;   // 32 KB: every rank's copy of one tile
+constexpr int kRbStages = 6;
+constexpr int kRbDepth = kRbStages - 1;
+constexpr int kRbSmemBytes = kRbStages * kRbStageBytes;
+constexpr int kRbTilesPerItem = kChunk / kRbTile;
+static_assert(kRbTile == kBulkThreads * 4 && kChunk % kRbTile == 0, "tile geometry");
+
+__device__ __forceinline__ bool reduce_bulk_eligible(uint32_t count, uint32_t fl) {
+    return count == (uint32_t)kChunk && (fl & kItemVec16) && !(fl & RLCU_TENSOR_GRAD_ZERO);
+}
+
+// Items the bulk path does not take (ragged tails, unaligned tensors): per-thread loads, the
+// ranks one after the other.  Rare, so simple.
+__device__ __forceinline__ void reduce_item_simple(const PeerIn& peers, __half* g, uint32_t count, uint32_t fl,
+                                                   float unscale, float (&acc)[4], float& probe, int threads) {
+    const int n = peers.n;
+    const bool bf = (fl & kItemBF16) != 0;
+    const ptrdiff_t base_off = g - peers.local_base;
+    const uint32_t groups = (fl & kItemVec16) ? count / kGroup : 0;
+    for (uint32_t grp = threadIdx.x; grp < groups; grp += threads) {
+        const ptrdiff_t off = base_off + (ptrdiff_t)grp * kGroup;
+        F8 sum = x8_to_f8(ld_h8(peers.base[0] + off), bf);
+        for (int j = 1; j < n; j++) add_h8(ld_h8(peers.base[j] + off), sum, bf);
+        const uint4 r = f8_to_x8(sum, bf);
+        *reinterpret_cast<uint4*>(g + (size_t)grp * kGroup) = r;
+        square_accumulate(x8_to_f8(r, bf), unscale, acc, probe);
+    }
+    for (uint32_t i = groups * kGroup + threadIdx.x; i < count; i += threads) {
+        float s = x_to_f(__half_as_ushort(peers.base[0][base_off + i]), bf);
+        for (int j = 1; j < n; j++) s = __fadd_rn(s, x_to_f(__half_as_ushort(peers.base[j][base_off + i]), bf));
+        const __half r = __ushort_as_half(f_to_x(s, bf));
+        g[i] = r;
+        const float raw = x_to_f(__half_as_ushort(r), bf);
+        probe = __fmaf_rn(raw, 0.0f, probe);
+        const float x = raw * unscale;
+        acc[0] = fmaf(x, x, acc[0]);
+    }
+}
+
+__global__ void __launch_bounds__(kBulkThreads + 32, 1)
+reduce_stat_bulk_kernel(const WorkItem* __restrict__ table, uint32_t n_items,
+                        const __grid_constant__ PeerIn peers, float unscale_arg,
+                        const rlcu_scaler_state* scaler, rlcu_stat* out, float* partials,
+                        unsigned int* counter, unsigned int* error_word) {
+    extern __shared__ __align__(128) unsigned char ring[];
+    __shared__ __align__(8) unsigned long long full_bar[kRbStages];
+    __shared__ __align__(8) unsigned long long empty_bar[kRbStages];
+    __shared__ float warp_sums[(kBulkThreads + 32) / 32];
+    __shared__ bool is_last;
+    float unscale = unscale_arg;
+    if (scaler) {
+        const float mul = scaler->grad_mul == 0.0f ? 1.0f : scaler->grad_mul;
+        unscale = __fmul_rn(mul, __fdiv_rn(1.0f, scaler->scale));
+    }
+    const int n = peers.n;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kRbStages; s++) {
+            mbar_init(smem_u32(&full_bar[s]), 1);                    // the producer's expect_tx
+            mbar_init(smem_u32(&empty_bar[s]), kBulkThreads / 32);   // one arrival per consumer warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float probe = 0.0f;
+    if (threadIdx.x >= kBulkThreads) {
+        // ---------------- producer: one thread issues every bulk load ----------------
+        if (threadIdx.x == kBulkThreads) {
+            uint32_t issued = 0;
+            bool bail = false;
+            for (uint32_t idx = blockIdx.x; idx < n_items && !bail; idx += gridDim.x) {
+                const WorkItem* wi = table + idx;
+                const uint4 a = __ldg(reinterpret_cast<const uint4*>(wi));
+                const uint4 d = __ldg(reinterpret_cast<const uint4*>(wi) + 2);
+                const uint4 e = __ldg(reinterpret_cast<const uint4*>(wi) + 3);
+                if (!reduce_bulk_eligible(d.z, e.x)) continue;
+                const __half* g = reinterpret_cast<const __half*>(((uint64_t)a.w << 32) | a.z);
+                const ptrdiff_t base_off = g - peers.local_base;
+                for (int sub = 0; sub < kRbTilesPerItem; sub++) {
+                    const int stage = issued % kRbStages;
+                    // the consumers are done with what this stage held kRbStages tiles ago
+                    if (issued >= (uint32_t)kRbStages &&
+                        !mbar_wait(smem_u32(&empty_bar[stage]), ((issued / kRbStages) - 1) & 1u)) {
+                        bail = true;
+                        break;
+                    }
+                    const uint32_t bar = smem_u32(&full_bar[stage]);
+                    const uint32_t dst = smem_u32(ring + (size_t)stage * kRbStageBytes);
+                    mbar_expect_tx(bar, (uint32_t)n * kRbTileBytes);
+                    for (int j = 0; j < n; j++)
+                        bulk_load(dst + j * kRbTileBytes, peers.base[j] + base_off + (ptrdiff_t)sub * kRbTile, kRbTileBytes, bar);
+                    issued++;
+                }
+            }
+            if (bail) atomicExch(error_word, 1u);
+            // Loads already issued land in this CTA's shared memory whatever the consumers do: the
+            // CTA must not end before they have (bounded waits on the stages still filling).
+            const uint32_t first = issued > (uint32_t)kRbStages ? issued - kRbStages : 0;
+            for (uint32_t t = first; t < issued; t++)
+                mbar_wait(smem_u32(&full_bar[t % kRbStages]), (t / kRbStages) & 1u);
+        }
+    } else {
+        // ---------------- consumers ----------------
+        uint32_t tiles = 0;
+        bool bail = false;
+        for (uint32_t idx = blockIdx.x; idx < n_items && !bail; idx += gridDim.x) {
+            const WorkItem* wi = table + idx;
+            const uint4 a = __ldg(reinterpret_cast<const uint4*>(wi));
+            const uint4 d = __ldg(reinterpret_cast<const uint4*>(wi) + 2);
+            const uint4 e = __ldg(reinterpret_cast<const uint4*>(wi) + 3);
+            __half* g = reinterpret_cast<__half*>(((uint64_t)a.w << 32) | a.z);
+            const uint32_t count = d.z, fl = e.x;
+            if (fl & RLCU_TENSOR_GRAD_ZERO) continue;
+            if (!reduce_bulk_eligible(count, fl)) {
+                reduce_item_simple(peers, g, count, fl, unscale, acc, probe, kBulkThreads);
+                continue;
+            }
+            const bool bf = (fl & kItemBF16) != 0;
+            for (int sub = 0; sub < kRbTilesPerItem; sub++) {
+                const int stage = tiles % kRbStages;
+                if (!mbar_wait(smem_u32(&full_bar[stage]), (tiles / kRbStages) & 1u)) {
+                    atomicExch(error_word, 1u);       // stop arriving: the producer's wait runs out too
+                    bail = true;
+                    break;
+                }
+                const unsigned char* st = ring + (size_t)stage * kRbStageBytes + (size_t)threadIdx.x * 8;
+                uint2 x = *reinterpret_cast<const uint2*>(st);
+                float s4[4];
+                {
+                    const uint32_t w[2] = {x.x, x.y};
+#pragma unroll
+                    for (int k = 0; k < 2; k++) {
+                        s4[2 * k] = x_to_f((unsigned short)(w[k] & 0xFFFFu), bf);
+                        s4[2 * k + 1] = x_to_f((unsigned short)(w[k] >> 16), bf);
+                    }
+                }
+                for (int j = 1; j < n; j++) {
+                    x = *reinterpret_cast<const uint2*>(st + (size_t)j * kRbTileBytes);
+                    const uint32_t w[2] = {x.x, x.y};
+#pragma unroll
+                    for (int k = 0; k < 2; k++) {
+                        s4[2 * k] = __fadd_rn(s4[2 * k], x_to_f((unsigned short)(w[k] & 0xFFFFu), bf));
+                        s4[2 * k + 1] = __fadd_rn(s4[2 * k + 1], x_to_f((unsigned short)(w[k] >> 16), bf));
+                    }
+                }
+                __syncwarp();
+                if ((threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
+                uint2 r;
+                r.x = (uint32_t)f_to_x(s4[0], bf) | ((uint32_t)f_to_x(s4[1], bf) << 16);
+                r.y = (uint32_t)f_to_x(s4[2], bf) | ((uint32_t)f_to_x(s4[3], bf) << 16);
+                *reinterpret_cast<uint2*>(g + (size_t)sub * kRbTile + (size_t)threadIdx.x * 4) = r;
+                const uint32_t rw[2] = {r.x, r.y};
+#pragma unroll
+                for (int k = 0; k < 2; k++) {
+                    const float lo = x_to_f((unsigned short)(rw[k] & 0xFFFFu), bf), hi = x_to_f((unsigned short)(rw[k] >> 16), bf);
+                    probe = __fmaf_rn(lo, 0.0f, probe);
+                    probe = __fmaf_rn(hi, 0.0f, probe);
+                    const float a0 = lo * unscale, a1 = hi * unscale;
+                    acc[2 * k] = fmaf(a0, a0, acc[2 * k]);
+                    acc[2 * k + 1] = fmaf(a1, a1, acc[2 * k + 1]);
+                }
+                tiles++;
+            }
+        }
+    }
+
+    // ---------------- the CTA's partial, then the last CTA's total ----------------
+    float mine = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    if (isnan(probe)) mine = __int_as_float(0x7FC00000);
+#pragma unroll
+    for (int mask = 16; mask >= 1; mask >>= 1) mine += __shfl_xor_sync(0xFFFFFFFFu, mine, mask);
+    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = mine;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.0f;
+        for (int w = 0; w < (kBulkThreads + 32) / 32; w++) total += warp_sums[w];
+        partials[blockIdx.x] = total;
+        __threadfence();
+        is_last = (atomicAdd(counter, 1u) == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (threadIdx.x < 32) {
+        double s = 0.0;
+        for (uint32_t i = threadIdx.x; i < gridDim.x; i += 32) s += (double)__ldcg(partials + i);
+#pragma unroll
+        for (int mask = 16; mask >= 1; mask >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, mask);
+        if (threadIdx.x == 0) {
+            *counter = 0;
+            out->sum_sq = s;      // this rank's share; the host code all-reduces it
+        }
+    }
+}
+
+// Clears share `part` of `parts` of the gradient pool outside the shard (RLCU_STEP_ZERO_GRADS).
+__device__ __forceinline__ void zero_slice(const ZeroSpan& z, uint64_t part, uint64_t parts) {
+    const uint64_t total = z.a_vecs + z.b_vecs;
+    const uint64_t lo = total * part / parts, hi = total * (part + 1) / parts;
+    for (uint64_t i = lo + threadIdx.x; i < hi; i += blockDim.x)
+        __stcs(i < z.a_vecs ? z.a + i : z.b + (i - z.a_vecs), make_uint4(0u, 0u, 0u, 0u));
+}
+
 __global__ void __launch_bounds__(kThreads)
 adamw_table_peer_kernel(const WorkItem* __restrict__ table, uint32_t n_items, StepConsts c,
                         const rlcu_stat* __restrict__ stat, uint32_t step_flags,
-                        const __grid_constant__ PeerOut peers) {
+                        const __grid_constant__ PeerOut peers, const __grid_constant__ ZeroSpan zero) {
     GradXform xf;
-    // a skipped (overflowed) step leaves parameters as they are on every rank, so
-    // there is nothing to deliver either
-    if (!resolve_step(stat, step_flags, c, xf)) return;
+    const bool clear = (step_flags & RLCU_STEP_ZERO_GRADS) != 0;
+    // a skipped (overflowed) step leaves parameters as they are on every rank, so there is
+    // nothing to deliver either; stale gradients are still cleared if that was asked for
+    if (!resolve_step(stat, step_flags, c, xf)) {
+        if (!clear) return;
+        clear_gradients(table, n_items);
+        zero_slice(zero, blockIdx.x, gridDim.x);
+        return;
+    }
     uint32_t idx = blockIdx.x;
     if (idx >= n_items) return;
     WorkItem next = load_item(table, idx);
@@ -217,9 +439,23 @@ adamw_table_peer_kernel(const WorkItem* __restrict__ table, uint32_t n_items, St
         const uint32_t nidx = idx + gridDim.x;
         if (nidx < n_items) next = load_item(table, nidx);
         process_item<true>(it, c, xf, peers);
+        if (clear) zero_slice(zero, idx, n_items);      // spread over the items: rides under the NVLink stores
         if (nidx >= n_items) break;
         idx = nidx;
     }
+}
+
+// The same pass with the traffic, the peers' copies included, issued by the bulk-copy engine:
+// each finished 4 KB tile of parameters leaves shared memory once per destination.
+__global__ void __launch_bounds__(kBulkThreads + 32, 1)
+adamw_table_bulk_peer_kernel(const WorkItem* __restrict__ table, uint32_t n_items, StepConsts c,
+                             const rlcu_stat* __restrict__ stat, uint32_t step_flags,
+                             unsigned int* error_word, const __grid_constant__ PeerOut peers,
+                             const __grid_constant__ ZeroSpan zero) {
+    bulk_table_body<true>(TableItems{table}, n_items, c, stat, step_flags, error_word, peers);
+    // the rest of the gradient pool (RLCU_STEP_ZERO_GRADS): by the consumer threads, after
+    // their tiles; the shard's own gradients were cleared tile by tile
+    if ((step_flags & RLCU_STEP_ZERO_GRADS) && threadIdx.x < kBulkThreads) zero_slice(zero, blockIdx.x, gridDim.x);
 }
 
 struct Geometry {
@@ -243,6 +479,10 @@ int geometry(Geometry* out) {
         RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&g.occ_reduce[3], reduce_stat_kernel<4>, kThreads, 0));
         RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&g.occ_reduce[4], reduce_stat_kernel<8>, kThreads, 0));
         RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&g.occ_update, adamw_table_peer_kernel, kThreads, 0));
+        RLCU_CUDA(cudaFuncSetAttribute(adamw_table_bulk_peer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kBulkSmemBytes));
+        RLCU_CUDA(cudaFuncSetAttribute(reduce_stat_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kRbSmemBytes));
         for (int occ : g.occ_reduce)
             if (occ < 1) return set_error(RLCU_ERR_CUDA, "kernel does not fit on an SM");
         if (g.occ_update < 1) return set_error(RLCU_ERR_CUDA, "kernel does not fit on an SM");
@@ -256,12 +496,22 @@ int geometry(Geometry* out) {
 }  // namespace
 
 int launch_reduce_stat(rlcu_tensor_list* list, const PeerIn& peers, float unscale,
-                       const rlcu_scaler_state* scaler, rlcu_stat* stat, cudaStream_t stream) {
+                       const rlcu_scaler_state* scaler, rlcu_stat* stat, bool bulk, cudaStream_t stream) {
     if (!list || !stat) return set_error(RLCU_ERR_INVALID, "null list or stat");
     if (peers.n < 1 || peers.n > kMaxWorld) return set_error(RLCU_ERR_INVALID, "world size %d not supported", peers.n);
     Geometry g;
     const int rc = geometry(&g);
     if (rc) return rc;
+    if (bulk) {
+        int grid = g.sms;
+        if (grid > list->grid_stat) grid = list->grid_stat;
+        if ((uint32_t)grid > list->n_items) grid = list->n_items ? (int)list->n_items : 1;
+        reduce_stat_bulk_kernel<<<grid, kBulkThreads + 32, kRbSmemBytes, stream>>>(
+            list->d_items, list->n_items, peers, unscale, scaler, stat, list->d_partials, list->d_counter,
+            list->d_counter + 16);
+        RLCU_CUDA(cudaGetLastError());
+        return RLCU_OK;
+    }
     // the scratch of the list was sized for the statistics kernel's grid; stay within it
     const int variant = peers.n == 1 ? 1 : peers.n == 2 ? 2 : peers.n == 4 ? 3 : peers.n == 8 ? 4 : 0;
     int grid = g.sms * g.occ_reduce[variant];
@@ -284,10 +534,17 @@ int launch_reduce_stat(rlcu_tensor_list* list, const PeerIn& peers, float unscal
 }
 
 int launch_update_peers(rlcu_tensor_list* list, const rlcu_hparams* hp, const rlcu_stat* stat,
-                        uint32_t step_flags, const PeerOut& peers, cudaStream_t stream) {
+                        uint32_t step_flags, const PeerOut& peers, const ZeroSpan& zero, cudaStream_t stream) {
     if (!list || !hp) return set_error(RLCU_ERR_INVALID, "null list or hparams");
     if (peers.n < 0 || peers.n > kMaxPeers) return set_error(RLCU_ERR_INVALID, "%d peers not supported", peers.n);
-    if (list->n_items == 0) return RLCU_OK;
+    if (list->n_items == 0) {
+        // a rank whose shard lies wholly in the padding still owns the clearing of its pool
+        if ((step_flags & RLCU_STEP_ZERO_GRADS) && zero.a_vecs + zero.b_vecs) {
+            RLCU_CUDA(cudaMemsetAsync(zero.a, 0, zero.a_vecs * 16, stream));
+            if (zero.b_vecs) RLCU_CUDA(cudaMemsetAsync(zero.b, 0, zero.b_vecs * 16, stream));
+        }
+        return RLCU_OK;
+    }
     Geometry g;
     const int rc = geometry(&g);
     if (rc) return rc;
@@ -297,8 +554,22 @@ int launch_update_peers(rlcu_tensor_list* list, const rlcu_hparams* hp, const rl
     c.lr = hp->lr; c.b1 = hp->beta1; c.b2 = hp->beta2; c.eps = hp->eps;
     c.bc1_inv = 1.0f / hp->bias_correction1;
     c.bc2_inv = 1.0f / hp->bias_correction2;
+    // same choice as the single-GPU update: shards that are mostly FP16 weights with FP32
+    // masters go through the bulk-copy kernel unless the caller says otherwise
+    if ((step_flags & RLCU_STEP_BULK_COPY) && (step_flags & RLCU_STEP_DIRECT))
+        return set_error(RLCU_ERR_INVALID, "RLCU_STEP_BULK_COPY and RLCU_STEP_DIRECT exclude each other");
+    if (!(step_flags & RLCU_STEP_DIRECT) && list->prefer_bulk) step_flags |= RLCU_STEP_BULK_COPY;
+    step_flags &= ~(uint32_t)RLCU_STEP_DIRECT;
+    if (step_flags & RLCU_STEP_BULK_COPY) {
+        grid = (uint32_t)g.sms > list->n_items ? (int)list->n_items : g.sms;
+        adamw_table_bulk_peer_kernel<<<grid, kBulkThreads + 32, kBulkSmemBytes, stream>>>(
+            list->d_items, list->n_items, c, stat, step_flags & ~(uint32_t)RLCU_STEP_BULK_COPY,
+            list->d_counter + 16, peers, zero);
+        RLCU_CUDA(cudaGetLastError());
+        return RLCU_OK;
+    }
     adamw_table_peer_kernel<<<grid, kThreads, 0, stream>>>(list->d_items, list->n_items, c, stat,
-                                                           step_flags, peers);
+                                                           step_flags, peers, zero);
     RLCU_CUDA(cudaGetLastError());
     return RLCU_OK;
 }

@@ -20,14 +20,26 @@ struct PeerIn {
     const __half* base[kMaxWorld];
 };
 
+// The part of this rank's gradient pool that lies outside its shard, as two runs of 16-byte
+// vectors (before and after the shard).  With RLCU_STEP_ZERO_GRADS the update kernel clears
+// it while it works: once the norm has been all-reduced no other rank reads this pool any
+// more, and the local HBM is mostly idle while the parameters cross NVLink.
+struct ZeroSpan {
+    uint4* a;
+    uint64_t a_vecs;
+    uint4* b;
+    uint64_t b_vecs;
+};
+
 // Fused reduce-scatter + statistics over this rank's shard; writes the rank's
 // share of the sum of squares to stat->sum_sq.
+// `bulk`: fetch the ranks' gradients with the bulk-copy engine instead of per-thread loads.
 int launch_reduce_stat(rlcu_tensor_list* list, const PeerIn& peers, float unscale,
-                       const rlcu_scaler_state* scaler, rlcu_stat* stat, cudaStream_t stream);
+                       const rlcu_scaler_state* scaler, rlcu_stat* stat, bool bulk, cudaStream_t stream);
 
 // Fused update + all-gather: the update pass with every new FP16 parameter also
 // stored into the peers' pools.
 int launch_update_peers(rlcu_tensor_list* list, const rlcu_hparams* hp, const rlcu_stat* stat,
-                        uint32_t step_flags, const PeerOut& peers, cudaStream_t stream);
+                        uint32_t step_flags, const PeerOut& peers, const ZeroSpan& zero, cudaStream_t stream);
 
 }  // namespace rlcu

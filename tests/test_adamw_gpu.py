@@ -61,6 +61,37 @@ def test_config1_ten_steps_fp16_master(pkg, O, torch):
     assert all(d.guards_intact() for d in dev.values())
 
 
+@pytest.mark.parametrize("tail", [0, 4099])
+def test_large_tensor_with_master_takes_the_bulk_copy_kernel(pkg, O, torch, tail):
+    """rlcu_adamw_fp16_master on a tensor large enough for the bulk-copy kernel (at least four
+    work items per SM), with and without a ragged last item: three steps against the CPU oracle
+    and the reference's own kernel, bit for bit, guard bytes intact, no bounded wait gave up."""
+    n, lr, b1, b2, eps, wd = 8192 * 700 + tail, 1e-4, 0.9, 0.999, 1e-8, 0.01
+    p0, _, m0, v0 = seeded_case(O, n, seed=3, warm=True)
+    host = dict(master=O.h2f(p0), p=p0.copy(), m=m0.copy(), v=v0.copy())
+    dev = {k: DevBuf(a, torch) for k, a in host.items()}
+    ref = {k: DevBuf(a, torch) for k, a in host.items()} if O.ref_available() else None
+    for t in range(1, 4):
+        g = fresh_grad(O, n, seed=3, step=t, g_std=1e-2)
+        gd = DevBuf(g, torch)
+        bc1, bc2 = O.bias_correction(b1, t), O.bias_correction(b2, t)
+        pkg.adamw_fp16_master(dev["master"].ptr, dev["p"].ptr, gd.ptr, dev["m"].ptr, dev["v"].ptr,
+                              n, lr, b1, b2, eps, wd, bc1, bc2)
+        O.adamw_fp16_master(host["master"], host["p"], g, host["m"], host["v"],
+                            lr, b1, b2, eps, wd, bc1, bc2, O.NVCC, 0)
+        if ref:
+            assert O.ref_lib().ref_launch_adamw_fp16(ref["master"].ptr, ref["p"].ptr, gd.ptr, ref["m"].ptr,
+                                                     ref["v"].ptr, n, lr, b1, b2, eps, wd, bc1, bc2, None) == 0
+        torch.cuda.synchronize()
+        assert gd.guards_intact() and np.array_equal(gd.get(), g)
+    assert pkg.lib().rlcu_tensor_list_check(None) == pkg.OK
+    got = {k: d.get() for k, d in dev.items()}
+    check_state(got, host)
+    if ref:
+        check_state(got, {k: d.get() for k, d in ref.items()})
+    assert all(d.guards_intact() for d in dev.values())
+
+
 def test_config1_masterless(pkg, O, torch):
     n, lr, b1, b2, eps, wd = 1 << 20, 1e-5, 0.9, 0.999, 1e-8, 0.01
     p0, _, m0, v0 = seeded_case(O, n, seed=0)

@@ -18,6 +18,13 @@ def test_reference_arm_prints_the_contract_line():
     assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
     assert line["e2e"] == {"value": line["value"], "unit": "params/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert line["steps"] == 2 and line["warmup"] == 3 and line["higher_is_better"] is True
+    # the same `config` object the GPU arm of the same command prints
+    sys.path.insert(0, ROOT)
+    import argparse
+    import bench
+    want = bench.config_for(argparse.Namespace(workload="qwen3-0.6b", gpus=1))
+    assert line["config"] == want and want["params"] == 596_049_920 and want["tensors"] == 310
+    assert line["scaling"] == "strong"
 
 
 def test_reference_arm_other_ranks_stay_silent():

@@ -30,6 +30,43 @@ def test_float_to_half_rounding(O):
     assert O.f2h(np.array([np.nan], np.float32))[0] & 0x7C00 == 0x7C00
 
 
+def test_hardware_half_conversions_equal_the_bit_level_definition(O):
+    """The timed loops of the oracle convert with the CPU's F16C instructions when they are
+    there; the bit-level functions stay the definition.  Every binary16 value one way, the
+    rounding cases of the test above plus NaN the other way, and one whole update both ways."""
+    if not O.hw_half_available():
+        pytest.skip("no F16C on this CPU: the loops already use the bit-level functions")
+    L = O.lib()
+    for h in range(65536):
+        a, b = L.orc_h2f(h), L.orc_h2f_hw(h)
+        assert (np.isnan(a) and np.isnan(b)) or np.float32(a).view(np.uint32) == np.float32(b).view(np.uint32), h
+    rng = np.random.default_rng(2)
+    h = np.arange(65536, dtype=np.uint16)
+    finite = np.sort(h[(h & 0x7C00) != 0x7C00].view(np.float16).astype(np.float64))
+    ties = ((finite[:-1] + finite[1:]) / 2).astype(np.float32)
+    xs = np.concatenate([rng.standard_normal(20_000).astype(np.float32) * np.float32(s) for s in (1e-8, 6e-5, 1.0, 7e4)]
+                        + [ties[::7], np.array([65504, 65519.996, 65520, np.inf, -np.inf, np.nan, 2.0 ** -25, 0.0, -0.0], np.float32)])
+    for x in xs:
+        assert L.orc_f2h(float(x)) == L.orc_f2h_hw(float(x)), x
+    n = 50_001
+    p = O.f2h(rng.standard_normal(n).astype(np.float32) * np.float32(0.02))
+    g = O.f2h(rng.standard_normal(n).astype(np.float32) * np.float32(1e-2))
+    out = []
+    try:
+        for on in (True, False):
+            O.use_hw_half(on)
+            e = dict(p=p.copy(), g=g, m=np.zeros(n, np.float32), v=np.zeros(n, np.float32), wd=0.01)
+            ts = O.make_tensors([e])
+            st = O.gradstat(ts, 1.0, 0.5)
+            O.multi_step(ts, O.HParams(1e-3, 0.9, 0.999, 1e-8, 0.1, 0.001), st, O.STEP_ROUND_CLIP_FP16)
+            out.append((st.sum_sq, e["p"].copy(), e["m"].copy(), e["v"].copy()))
+    finally:
+        O.use_hw_half(True)
+    assert out[0][0] == out[1][0]
+    for a, b in zip(out[0][1:], out[1][1:]):
+        assert np.array_equal(a.view(np.uint8), b.view(np.uint8))
+
+
 def test_bias_correction_matches_float32_powf(O):
     """include/training/optimizer.h:121-122: 1.0f - powf(beta, (float)t), all in FP32."""
     for beta in (0.9, 0.999, 0.95, 0.8):
@@ -178,3 +215,60 @@ def test_scaler_state_machine(O):
     for i in range(40):
         O.scaler_update(s, 1 if i % 4 == 3 else 0, 1000)
     assert s.scale == 65536.0 / 2 ** 10 and s.step == 30 and s.skipped == 10
+
+
+def test_fp32_gradient_branch_equals_the_fp16_branch_on_exact_values(O):
+    """A 16-bit parameter with an FP32 gradient (ORC_GRAD_F32): with gradients that are exactly
+    representable in FP16 and no clip re-rounding, the statistics and the update equal those of
+    the FP16-gradient branch bit for bit; with the clip active the FP32 branch skips the FP16
+    re-rounding (trainer.h:142-145 against :136-139)."""
+    rng = np.random.default_rng(5)
+    n = 20_011
+    p = O.f2h(rng.standard_normal(n).astype(np.float32) * np.float32(0.02))
+    g16 = O.f2h(rng.standard_normal(n).astype(np.float32) * np.float32(1e-2))
+    g32 = O.h2f(g16)
+    hp = O.HParams(1e-3, 0.9, 0.999, 1e-8, O.bias_correction(0.9, 2), O.bias_correction(0.999, 2))
+
+    def run(grad, grad_dtype, max_norm, flags, master):
+        e = dict(p=p.copy(), g=grad, m=np.full(n, 1e-4, np.float32), v=np.full(n, 1e-6, np.float32), wd=0.01,
+                 dtype=O.F16, grad_dtype=grad_dtype)
+        if master:
+            e["master"] = O.h2f(p)
+        ts = O.make_tensors([e])
+        st = O.gradstat(ts, 1.0, max_norm)
+        O.multi_step(ts, hp, st, flags)
+        return st, e
+
+    for master in (False, True):
+        sa, a = run(g16, O.GRAD_AS_PARAM, 0.0, 0, master)
+        sb, b = run(g32, O.GRAD_F32, 0.0, 0, master)
+        assert (sa.sum_sq, sa.norm, sa.coef) == (sb.sum_sq, sb.norm, sb.coef)
+        for k in ("p", "m", "v") + (("master",) if master else ()):
+            assert np.array_equal(a[k].view(np.uint8), b[k].view(np.uint8)), k
+        # clip active: identical without the re-rounding flag, different with it (FP16 branch only)
+        sa, a = run(g16, O.GRAD_AS_PARAM, 0.5, 0, master)
+        sb, b = run(g32, O.GRAD_F32, 0.5, O.STEP_ROUND_CLIP_FP16, master)
+        assert sa.clip_active == sb.clip_active == 1
+        assert np.array_equal(a["m"].view(np.uint8), b["m"].view(np.uint8))
+        sc, c = run(g16, O.GRAD_AS_PARAM, 0.5, O.STEP_ROUND_CLIP_FP16, master)
+        assert not np.array_equal(c["m"].view(np.uint8), b["m"].view(np.uint8))
+
+
+def test_overflow_is_judged_on_the_stored_gradient(O):
+    """found_inf looks at the gradient element, not at its square: 1e20 in an FP32 gradient is
+    finite; its square is not, so the sum and the norm are +inf and a clip scales to zero."""
+    g = np.full(100, 1e-3, np.float32)
+    g[7] = 1e20
+    e = dict(p=np.zeros(100, np.float32), g=g, m=np.zeros(100, np.float32), v=np.zeros(100, np.float32))
+    st = O.gradstat(O.make_tensors([e]), 1.0, 1.0)
+    assert st.found_inf == 0 and np.isinf(st.sum_sq) and np.isinf(st.norm) and st.clip_active == 1 and st.coef == 0.0
+    st = O.gradstat(O.make_tensors([e]), 1.0, 0.0)
+    assert st.found_inf == 0 and st.clip_active == 0 and st.coef == 1.0
+    g[8] = np.inf
+    st = O.gradstat(O.make_tensors([e]), 1.0, 1.0)
+    assert st.found_inf == 1
+    h = np.full(64, 0x3C00, np.uint16)
+    h[3] = 0x7E00                                     # NaN in FP16
+    e16 = dict(p=h.copy(), g=h, m=np.zeros(64, np.float32), v=np.zeros(64, np.float32))
+    st = O.gradstat(O.make_tensors([e16]), 1.0, 1.0)
+    assert st.found_inf == 1 and st.sum_sq == 63.0    # the non-finite element is left out of the sum

@@ -540,6 +540,33 @@ def test_bulk_copy_update_equals_the_direct_update(pkg, O, torch, extra):
             assert np.array_equal(a[k].view(np.uint8), b[k].view(np.uint8)), k
 
 
+def test_master_lists_default_to_the_bulk_copy_kernel_with_the_same_bits(pkg, O, torch):
+    """A list that is mostly FP16 weights with FP32 masters and has at least four work items per
+    SM runs through the bulk-copy kernel unless RLCU_STEP_DIRECT is given; both give the bits
+    of the oracle."""
+    specs = [(8192 * 400 + 11, "hm", 0.01, 0), (8192 * 300, "hm", 0.0, 0), (5000, "f", 0.0, 0), (8192 * 20 + 3, "h", 0.01, 0)]
+    results = []
+    for forced in (0, pkg.STEP_DIRECT):
+        host, dev, descs = make_case(O, torch, pkg, specs, seed=171)
+        tl = pkg.TensorList(descs)
+        stat = torch.zeros(16, device="cuda")
+        hp = pkg.hparams(1e-4, 0.9, 0.999, 1e-8, 3)
+        tl.gradstat(stat.data_ptr(), 1.0, 1.0)
+        tl.step(hp, stat.data_ptr(), pkg.STEP_ROUND_CLIP_FP16 | forced)
+        tl.check()
+        got = read_stat(pkg, stat)
+        ot = O.make_tensors(host)
+        O.multi_step(ot, O.HParams(1e-4, 0.9, 0.999, 1e-8, hp.bias_correction1, hp.bias_correction2),
+                     O.gradstat_finalize(got.sum_sq, 0, 1.0, 1.0), O.STEP_ROUND_CLIP_FP16)
+        assert_same(host, dev)
+        results.append([{k: b.get() for k, b in d.items()} for d in dev])
+    for a, b in zip(*results):
+        for k in a:
+            assert np.array_equal(a[k].view(np.uint8), b[k].view(np.uint8)), k
+    with pytest.raises(pkg.RlcuError):
+        tl.step(hp, stat.data_ptr(), pkg.STEP_DIRECT | pkg.STEP_BULK_COPY)
+
+
 @pytest.mark.parametrize("side_stream", [False, True])
 def test_bounded_wait_gives_up_and_reports(pkg, torch, side_stream):
     """A device-side wait that nothing satisfies runs out of tries, the kernel returns, the host

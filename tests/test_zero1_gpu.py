@@ -43,7 +43,7 @@ def _inputs(O, world, bf=False):
     return total, p, m, v, grads
 
 
-def _run_rank(rank, world, uid, pkg, O, torch, use_master, mode=0, bf=False):
+def _run_rank(rank, world, uid, pkg, O, torch, use_master, mode=0, bf=False, extra_flags=0):
     """Runs one sharded step on this process's GPU; returns host copies of everything."""
     total, p, m, v, grads = _inputs(O, world, bf)
     plan = pkg.zero1_plan(SEGS, rank, world)
@@ -67,7 +67,7 @@ def _run_rank(rank, world, uid, pkg, O, torch, use_master, mode=0, bf=False):
     z = pkg.Zero1(uid, rank, world, p_pool.data_ptr(), g_pool.data_ptr(), SEGS, m_sh.data_ptr(), v_sh.data_ptr(),
                   master_sh.data_ptr() if use_master else None, mode=mode | (pkg.ZERO1_POOLS_BF16 if bf else 0))
     hp = pkg.hparams(LR, B1, B2, EPS, T)
-    z.step(hp, stat.data_ptr(), 1.0, MAX_NORM, None, pkg.STEP_ROUND_CLIP_FP16)
+    z.step(hp, stat.data_ptr(), 1.0, MAX_NORM, None, pkg.STEP_ROUND_CLIP_FP16 | extra_flags)
     torch.cuda.synchronize()
     z.poll_error()
     out = dict(p=p_pool.cpu().numpy().view(np.uint16), g=g_pool.cpu().numpy().view(np.uint16),
@@ -460,3 +460,83 @@ def test_create_fails_on_every_rank_when_one_rank_cannot_set_up(pkg, tmp_path):
     m0, m1 = ((tmp_path / f"create{r}.txt").read_text() for r in range(2))
     assert "another rank failed" in m0
     assert "32-byte aligned" in m1
+
+
+def _flags_worker(rank, world, port, out_dir, mode, extra_flags):
+    """The same step twice, without and with `extra_flags`, each on fresh buffers."""
+    import sys
+    import torch
+    import torch.distributed as dist
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    sys.path.insert(0, os.path.join(root, "tests"))
+    import __graft_entry__ as entry
+    from oracle import oracle as O
+    pkg = entry.load_package()
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    for tag, fl in (("plain", 0), ("flagged", extra_flags)):
+        box = [pkg.zero1_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        out = _run_rank(rank, world, box[0], pkg, O, torch, False, mode, False, fl)
+        np.savez(os.path.join(out_dir, f"{tag}{rank}.npz"), **out)
+        dist.barrier()
+    dist.destroy_process_group()
+
+
+def _compare_flag_runs(pkg, tmp_path, world, grads_cleared, same_sum_order=True):
+    """same_sum_order False: the flagged run adds the squares in another order (another kernel
+    with another partition of the shard), so its sum may differ in the last bits: the norm is
+    held to 1e-6 relative, and p, m, v to bit identity only if the clip factor came out equal."""
+    for r in range(world):
+        a, b = np.load(tmp_path / f"plain{r}.npz"), np.load(tmp_path / f"flagged{r}.npz")
+        sa, sb = pkg.Stat.from_buffer_copy(a["stat"].tobytes()), pkg.Stat.from_buffer_copy(b["stat"].tobytes())
+        if same_sum_order:
+            assert np.array_equal(a["stat"].view(np.uint8), b["stat"].view(np.uint8)), f"rank {r}: record differs"
+        else:
+            assert abs(sa.norm - sb.norm) <= 1e-6 * sa.norm and (sa.found_inf, sa.clip_active) == (sb.found_inf, sb.clip_active)
+        for k in ("p", "m", "v"):
+            if sa.coef == sb.coef:
+                assert np.array_equal(a[k].view(np.uint8), b[k].view(np.uint8)), f"rank {r}: {k} differs"
+            elif a[k].dtype == np.uint16:
+                assert ulp16(a[k], b[k]).max() <= 1, f"rank {r}: {k} differs by more than 1 ulp"
+            else:
+                assert np.all(np.abs(a[k] - b[k]) <= 1e-6 * np.abs(a[k]) + 1e-30), f"rank {r}: {k} differs"
+        if grads_cleared:
+            assert not b["g"].any(), f"rank {r}: gradient pool not cleared"
+            assert a["g"].any()
+        else:
+            assert np.array_equal(a["g"], b["g"])
+
+
+@pytest.mark.parametrize("mode", [0, 1], ids=["nccl", "p2p"])
+@pytest.mark.parametrize("world", [1, 2])
+def test_sharded_step_clears_the_whole_gradient_pool_when_asked(pkg, O, tmp_path, world, mode):
+    """RLCU_STEP_ZERO_GRADS in the sharded step (RL.cu's qwen3_gradients_zero, qwen3.cu:1109-1112,
+    folded in): same parameters, moments and record as without it, and every element of every
+    rank's gradient pool, inside and outside its shard, is zero afterwards."""
+    import torch
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    mp.spawn(_flags_worker, args=(world, _free_port(), str(tmp_path), mode, pkg.STEP_ZERO_GRADS), nprocs=world, join=True)
+    _compare_flag_runs(pkg, tmp_path, world, grads_cleared=True)
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_sharded_step_through_the_bulk_copy_engine(pkg, O, tmp_path, world):
+    """RLCU_STEP_BULK_COPY in peer-to-peer mode: the peers' gradients are fetched, and the update's
+    traffic (the copies into the peers' pools included) is issued, by cp.async.bulk.  Reduced
+    gradients are bit-identical to the direct kernels'; the sum of squares is taken in another
+    order."""
+    import torch
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    mp.spawn(_flags_worker, args=(world, _free_port(), str(tmp_path), 1, pkg.STEP_BULK_COPY), nprocs=world, join=True)
+    _compare_flag_runs(pkg, tmp_path, world, grads_cleared=False, same_sum_order=False)
+    mp.spawn(_flags_worker, args=(world, _free_port(), str(tmp_path), 1, pkg.STEP_BULK_COPY | pkg.STEP_ZERO_GRADS),
+             nprocs=world, join=True)
+    _compare_flag_runs(pkg, tmp_path, world, grads_cleared=True, same_sum_order=False)
