@@ -782,6 +782,20 @@ def run_sharded(args):
         phase_ms = {"reduce_scatter": timed(1, ks), "statistics_allreduce": timed(2, ks),
                     "update": timed(4, ks), "all_gather": timed(8, ks)}
 
+    if args.quick:                     # device-resident timing only (sweeps, profiler runs)
+        if rank == 0:
+            wire = 2.0 * P * (world - 1) / world
+            print(json.dumps({"metric": "adamw_params_per_sec", "value": P / (ms_per_step * 1e-3), "unit": "params/s",
+                              "n_gpus": world, "steps": K, "warmup": args.warmup, "ms_per_step": ms_per_step,
+                              "phases_ms": phase_ms, "config": config_for(args), "quick": True,
+                              "link_gbs_per_direction": {k: wire / (v * 1e-3) / 1e9 for k, v in phase_ms.items()
+                                                         if "reduce_scatter" in k or "gather" in k},
+                              "env": {k: v for k, v in os.environ.items() if k.startswith("RLCU_")}}), flush=True)
+        z.close()
+        dist.barrier()
+        dist.destroy_process_group()
+        return
+
     # end to end: this rank's gradient replica comes from pinned host memory every step
     host_g = torch.empty(padded, dtype=torch.float16).pin_memory()
     host_g.copy_(g_fresh)

@@ -23,6 +23,7 @@ constexpr int kBulkDepth = kBulkStages - 2;           // tiles loading ahead of 
 constexpr int kBulkStageBytes = 32768;                // [m 8K][v 8K][master 8K][p 4K][g 4K]
 constexpr int kBulkSmemBytes = kBulkStages * kBulkStageBytes;
 constexpr uint32_t kBulkWaitTries = 1u << 18;
+constexpr int kBulkPendingCap = 1024;                 // items per CTA remembered for the direct code
 static_assert(kChunk % kBulkTile == 0 && kBulkTile == kBulkThreads * 4, "tile geometry");
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -200,6 +201,7 @@ __device__ __forceinline__ void bulk_table_body(const Items items, uint32_t n_it
     extern __shared__ __align__(128) unsigned char ring[];
     __shared__ __align__(8) unsigned long long full_bar[kBulkStages];
     __shared__ __align__(8) unsigned long long empty_bar[kBulkStages];
+    __shared__ uint32_t pending[kBulkPendingCap];     // items left to the direct code
     GradXform xf;
     if (!resolve_step(stat, step_flags, c, xf)) {
         if (!(step_flags & RLCU_STEP_ZERO_GRADS)) return;
@@ -272,24 +274,42 @@ __device__ __forceinline__ void bulk_table_body(const Items items, uint32_t n_it
     }
 
     // ---------------- consumer warps ----------------
-    uint32_t tiles = 0;
-    for (uint32_t idx = blockIdx.x; idx < n_items; idx += gridDim.x) {
+    // The items that go through the ring first; the ones that do not (partial items, FP32
+    // tensors) are noted on the way and run afterwards with the direct code, which keeps that
+    // code's registers out of the tile loop.
+    uint32_t tiles = 0, n_pending = 0;       // n_pending is the same in every consumer thread
+    bool ok = true;
+    for (uint32_t idx = blockIdx.x; idx < n_items && ok; idx += gridDim.x) {
         const WorkItem it = items.get(idx);
         if (!bulk_eligible(it)) {
-            if (threadIdx.x < kThreads) process_item<PEERS>(it, c, xf, peers);
+            if (threadIdx.x == 0 && n_pending < (uint32_t)kBulkPendingCap) pending[n_pending] = idx;
+            n_pending++;
             continue;
         }
         for (int sub = 0; sub < kBulkTilesPerItem; sub++) {
             const int stage = tiles % kBulkStages;
             if (!mbar_wait(smem_u32(&full_bar[stage]), (tiles / kBulkStages) & 1u)) {
                 atomicExch(error_word, 1u);      // stop arriving: the producer's wait runs out too
-                return;
+                ok = false;
+                break;
             }
             bulk_compute_tile(it, ring + (size_t)stage * kBulkStageBytes, c, xf);
             fence_async_smem();                  // results visible to the bulk store
             __syncwarp();
             if ((threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
             tiles++;
+        }
+    }
+    // consumer-only barrier: the list written by thread 0 is visible to the others
+    asm volatile("bar.sync 1, %0;" :: "n"(kBulkThreads) : "memory");
+    if (!ok || threadIdx.x >= kThreads) return;      // the direct code is written for kThreads threads
+    const uint32_t listed = n_pending < (uint32_t)kBulkPendingCap ? n_pending : (uint32_t)kBulkPendingCap;
+    for (uint32_t i = 0; i < listed; i++) process_item<PEERS>(items.get(pending[i]), c, xf, peers);
+    if (n_pending > listed) {
+        // more than the list holds: walk the rest of this CTA's items again
+        for (uint32_t idx = pending[listed - 1] + gridDim.x; idx < n_items; idx += gridDim.x) {
+            const WorkItem it = items.get(idx);
+            if (!bulk_eligible(it)) process_item<PEERS>(it, c, xf, peers);
         }
     }
 }

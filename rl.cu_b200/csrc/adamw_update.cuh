@@ -199,7 +199,15 @@ __device__ __forceinline__ void vector_item(const WorkItem& it, const StepConsts
             else f16_groups<KIND, V32, ROUND, U, PEERS, GF32>(it, first, kThreads, c, decay, xf, peers);
         }
     } else {
-        for (int grp = threadIdx.x; grp < groups; grp += kThreads) {
+        // partial item (the head or the tail of a tensor): kUnroll groups per thread at a time
+        // while that many are left, then one at a time, then the last few elements one by one
+        constexpr int U = kUnroll;
+        int grp = threadIdx.x;
+        for (; grp + (U - 1) * kThreads < groups; grp += U * kThreads) {
+            if constexpr (KIND == 2) f32_groups<V32, U>(it, grp, kThreads, c, decay, xf);
+            else f16_groups<KIND, V32, ROUND, U, PEERS, GF32>(it, grp, kThreads, c, decay, xf, peers);
+        }
+        for (; grp < groups; grp += kThreads) {
             if constexpr (KIND == 2) f32_groups<V32, 1>(it, grp, 0, c, decay, xf);
             else f16_groups<KIND, V32, ROUND, 1, PEERS, GF32>(it, grp, 0, c, decay, xf, peers);
         }

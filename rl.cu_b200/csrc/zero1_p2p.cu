@@ -14,6 +14,7 @@
 // small NCCL collectives the host code enqueues around them (zero1.cu).
 #include "zero1_p2p.h"
 
+#include <cstdlib>
 #include <mutex>
 
 #include "adamw_bulk.cuh"
@@ -149,7 +150,11 @@ reduce_stat_kernel(const WorkItem* __restrict__ table, uint32_t n_items,
         bool wide = count == kChunk;
         for (int j = 0; j < n; j++) wide = wide && ((reinterpret_cast<uintptr_t>(peers.base[j] + base_off) & 31) == 0);
         if (wide) {
+#ifdef RLCU_RS_WIDE_UB
+            constexpr int UB = RLCU_RS_WIDE_UB;
+#else
             constexpr int UB = WORLD == 8 ? 1 : 2;       // 512 wide groups per item, 2 per thread
+#endif
 #pragma unroll
             for (int b = 0; b < 2 / UB; b++) {
                 const ptrdiff_t first = (ptrdiff_t)(threadIdx.x + b * UB * kThreads) * 16;
@@ -166,8 +171,16 @@ reduce_stat_kernel(const WorkItem* __restrict__ table, uint32_t n_items,
             }
             continue;
         }
-        for (uint32_t grp = threadIdx.x; grp < groups; grp += kThreads)
-            reduce_groups<WORLD, 1>(peers, base_off + (ptrdiff_t)grp * kGroup, g + (size_t)grp * kGroup, 0, unscale, acc, bf, probe);
+        // partial item (head or tail of a tensor): batches of groups while enough are left
+        {
+            constexpr int UB = ReduceBatch<WORLD>::value;
+            uint32_t grp = threadIdx.x;
+            for (; grp + (UB - 1) * kThreads < groups; grp += UB * kThreads)
+                reduce_groups<WORLD, UB>(peers, base_off + (ptrdiff_t)grp * kGroup, g + (size_t)grp * kGroup, kThreads,
+                                         unscale, acc, bf, probe);
+            for (; grp < groups; grp += kThreads)
+                reduce_groups<WORLD, 1>(peers, base_off + (ptrdiff_t)grp * kGroup, g + (size_t)grp * kGroup, 0, unscale, acc, bf, probe);
+        }
         for (uint32_t i = groups * kGroup + threadIdx.x; i < count; i += kThreads) {
             float s = x_to_f(__half_as_ushort(peers.base[0][base_off + i]), bf);
             for (int j = 1; j < n; j++) s = __fadd_rn(s, x_to_f(__half_as_ushort(peers.base[j][base_off + i]), bf));
@@ -486,6 +499,16 @@ int geometry(Geometry* out) {
         for (int occ : g.occ_reduce)
             if (occ < 1) return set_error(RLCU_ERR_CUDA, "kernel does not fit on an SM");
         if (g.occ_update < 1) return set_error(RLCU_ERR_CUDA, "kernel does not fit on an SM");
+        // measurement knobs: cap the resident CTAs per SM of the two exchange kernels
+        if (const char* e = getenv("RLCU_P2P_REDUCE_CTAS_PER_SM")) {
+            const int cap = atoi(e);
+            for (int& occ : g.occ_reduce)
+                if (cap >= 1 && cap < occ) occ = cap;
+        }
+        if (const char* e = getenv("RLCU_P2P_UPDATE_CTAS_PER_SM")) {
+            const int cap = atoi(e);
+            if (cap >= 1 && cap < g.occ_update) g.occ_update = cap;
+        }
         cache[dev] = g;
         have[dev] = true;
     }
