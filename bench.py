@@ -292,10 +292,14 @@ def time_variants(torch, pkg, pools, shapes, wd, hp, stat, stream, peak, only=""
     out = {}
     want = lambda name: not only or name in only.split(",")
 
-    def entry(ms, bytes_per_param, params, what, launches):
+    def entry(ms, bytes_per_param, params, what, launches, ncu_key=None):
         gbs = bytes_per_param * params / (ms * 1e-3) / 1e9
-        return {"ms": ms, "bytes_per_param": bytes_per_param, "params": params, "launches_per_step": launches,
-                "achieved_gbs": gbs, "frac_of_measured": gbs / peak, "what": what}
+        e = {"ms": ms, "bytes_per_param": bytes_per_param, "params": params, "launches_per_step": launches,
+             "achieved_gbs": gbs, "frac_of_measured": gbs / peak, "what": what}
+        per_param = ncu_dram_bytes_per_param(ncu_key) if ncu_key else None
+        if per_param is not None:
+            e["traffic"] = per_param * params          # DRAM bytes per step, from the ncu capture of this kernel
+        return e
 
     def descs(master=None, g32=None, align=8):
         d, off = [], 0
@@ -314,8 +318,11 @@ def time_variants(torch, pkg, pools, shapes, wd, hp, stat, stream, peak, only=""
     if want("multi_tensor_fp32_master") or want("bulk_copy_fp32_master"):
         tl = pkg.TensorList(descs(master=master))
         ms = mean_launch_ms(torch, lambda: tl.step(hp, stat.data_ptr(), pkg.STEP_ROUND_CLIP_FP16, stream=stream))
-        out["multi_tensor_fp32_master"] = entry(ms, 28, P, "adamw_table_kernel, FP16 weights written from an FP32 master "
-                                                "(read master,g,m,v; write master,p,m,v)", 1)
+        out["multi_tensor_fp32_master"] = entry(ms, 28, P, "the kernel rlcu_adamw_multi_step picks for this list (adamw_table_bulk_kernel), "
+                                                "FP16 weights written from an FP32 master (read master,g,m,v; write master,p,m,v)",
+                                                1, "adamw_table_bulk_kernel_fp32_master")
+        ms = mean_launch_ms(torch, lambda: tl.step(hp, stat.data_ptr(), pkg.STEP_ROUND_CLIP_FP16 | pkg.STEP_DIRECT, stream=stream))
+        out["direct_fp32_master"] = entry(ms, 28, P, "adamw_table_kernel (per-thread loads and stores) forced on the same list", 1)
         ms = mean_launch_ms(torch, lambda: tl.step(hp, stat.data_ptr(), pkg.STEP_ROUND_CLIP_FP16 | pkg.STEP_BULK_COPY, stream=stream))
         tl.check()
         out["bulk_copy_fp32_master"] = entry(ms, 28, P, "adamw_table_bulk_kernel with an FP32 master", 1)
@@ -342,8 +349,8 @@ def time_variants(torch, pkg, pools, shapes, wd, hp, stat, stream, peak, only=""
         ms = mean_launch_ms(torch, three_launches)
         out["reference_layout_three_launches"] = entry(
             ms, 28, n_proj + n_embed + n32,
-            f"adamw_flat_kernel behind launch_adamw_fp16 x2 ({n_proj} + {n_embed} elements) and "
-            f"launch_adamw_fp32 ({n32}), as AdamWOptimizer::step issues them", 3)
+            f"adamw_flat_bulk_kernel behind launch_adamw_fp16 x2 ({n_proj} + {n_embed} elements) and "
+            f"launch_adamw_fp32 ({n32}), as AdamWOptimizer::step issues them", 3, "adamw_flat_bulk_kernel")
     # (iii) the bulk-copy (cp.async.bulk) form of the multi-tensor kernel
     if want("bulk_copy"):
         tl = pkg.TensorList(descs())
@@ -660,7 +667,7 @@ def checked_step(torch, dist, pkg, z, mode, rank, world, segments, P, S, p_pool,
     out["grad_norm"] = rec.norm
     out["clip_active"] = int(rec.clip_active)
     out["ok"] = bool(out["ranks_agree"] and int(flag[0]) == 1 and out["norm_rel_err"] <= 1e-5 and
-                     out["sum_sq_rel_err_vs_single_gpu_kernels"] <= 1e-6 and rec.found_inf == 0)
+                     out["sum_sq_rel_err_vs_single_gpu_kernels"] <= 1e-5 and rec.found_inf == 0)
     tl.close()
     return out
 
@@ -728,7 +735,7 @@ def run_sharded(args):
         z = create(mode)
     stream = torch.cuda.current_stream().cuda_stream
     lr, b1, b2, eps, max_norm = 1e-6, 0.9, 0.999, 1e-8, 1.0
-    flags = pkg.STEP_ROUND_CLIP_FP16 | (pkg.STEP_BULK_COPY if args.bulk else 0)
+    flags = pkg.STEP_ROUND_CLIP_FP16 | (pkg.STEP_BULK_COPY if args.bulk else 0) | (pkg.STEP_DIRECT if args.direct else 0)
 
     def step(t, phases=0):
         z.step(pkg.hparams(lr, b1, b2, eps, t), stat.data_ptr(), 1.0, max_norm, None, flags, phases, stream)
@@ -840,6 +847,7 @@ def run_sharded(args):
         tl_sh = shard_list()
         shard_ms = mean_launch_ms(torch, lambda: tl_sh.step(hp_now, stat.data_ptr(), flags, stream=stream), reps=10)
         tl_sh.close()
+        torch.cuda.empty_cache()
         m_full = torch.zeros(P, dtype=torch.float32, device=dev)
         v_full = torch.zeros(P, dtype=torch.float32, device=dev)
         descs, off = [], 0
@@ -879,7 +887,7 @@ def run_sharded(args):
                           "update_allgather_fused": wire / (phase_ms["update_allgather_fused"] * 1e-3) / 1e9}
             upd_ms = phase_ms["update_allgather_fused"]
             roof = {"bound": "nvlink" if wire / link > upd_bytes / peak else "hbm",
-                    "kernel": "adamw_table_peer_kernel (shard update + all-gather)",
+                    "kernel": ("adamw_table_peer_kernel" if args.direct else "adamw_table_bulk_peer_kernel") + " (shard update + all-gather)",
                     "achieved": link_rates["update_allgather_fused"], "peak": link,
                     "peak_kind": "measured peer copy, GB/s per direction per GPU", "unit": "GB/s",
                     "frac": link_rates["update_allgather_fused"] / link,
@@ -899,7 +907,8 @@ def run_sharded(args):
             "dtype": "f32", "storage": "f16 params and grads, f32 moments", "data": "synthetic",
             "config": config_for(args),
             "run_info": {"shard_params": S,
-                         "exchange": ("peer-to-peer kernels over NVLink: fused reduce-scatter+statistics, fused update+all-gather, "
+                         "exchange": ("peer-to-peer kernels over NVLink: fused reduce-scatter+statistics, fused update+all-gather "
+                                      f"({'per-thread loads and stores' if args.direct else 'cp.async.bulk through shared memory'}), "
                                       "8-byte NCCL all-reduces for ordering and the norm") if mode == pkg.ZERO1_P2P else
                                      "ncclReduceScatter(sum, f16) + ncclAllReduce(1 double) + ncclAllGather(f16)",
                          "grad_restore": "device copy of the rank's gradient replica before each step, outside the timed intervals",
@@ -974,6 +983,8 @@ def main():
                     help="N=1: elements every tensor start is aligned to inside the pools (8 = 16 bytes)")
     ap.add_argument("--bulk", action="store_true",
                     help="N=1: run the update through the cp.async.bulk variant of the kernel")
+    ap.add_argument("--direct", action="store_true",
+                    help="N>1: force the per-thread load/store exchange kernels (the default for FP16 pools is the bulk-copy pair)")
     ap.add_argument("--variants", default="", help="with --quick: also time these variants of the update (comma-separated "
                     "names of the `variants` object: multi_tensor_fp32_master, reference_layout_three_launches, bulk_copy, fp32_gradients)")
     ap.add_argument("--quick", action="store_true",

@@ -239,7 +239,10 @@ uint64_t rlcu_tensor_list_work_items(const rlcu_tensor_list* list);
  *               grad_mul/scale from it (the `unscale` argument is ignored) and the
  *               finished record also carries the step's bias corrections, after
  *               which the scale / step counter are advanced.
- * Calls on the same list must not overlap on the GPU (they share its scratch). */
+ * Calls on the same list must not overlap on the GPU (they share its scratch).
+ * The sum is taken in a fixed order for a given list, so the same list gives the same bits run
+ * after run; the order follows the work items, which are cut by address, so a copy of the same
+ * data at other addresses may differ in the last bits of sum_sq. */
 int rlcu_gradstat(rlcu_tensor_list* list, float unscale, float max_norm,
                   rlcu_scaler_state* scaler, rlcu_stat* stat_out, uint32_t flags, void* stream);
 /* The statistics pass for callers that cannot allocate device memory: one flat
@@ -355,8 +358,10 @@ int rlcu_zero1_create(const void* unique_id, int rank, int world,
  * reduce-scatter + statistics, 2 all-reduce + finalize, 4 (or 8) fused update +
  * all-gather.  With RLCU_STEP_ZERO_GRADS the whole local gradient pool is zero after the step
  * (in P2P mode cleared inside the update kernel, under its NVLink traffic).
- * RLCU_STEP_BULK_COPY moves the update's traffic, the peers' copies in P2P mode included,
- * with the bulk-copy engine (FP16 pools only; bfloat16 pools take the direct path). */
+ * In P2P mode with FP16 pools on more than one rank the two exchange kernels move their NVLink
+ * traffic with the bulk-copy engine (cp.async.bulk, no multicast) by default, which is 1-2 %
+ * faster than per-thread loads and stores; RLCU_STEP_DIRECT forces the latter (bfloat16 pools
+ * always use it), RLCU_STEP_BULK_COPY the former. */
 int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float max_norm,
                     rlcu_scaler_state* scaler, rlcu_stat* stat, uint32_t step_flags,
                     uint32_t phases, void* stream);

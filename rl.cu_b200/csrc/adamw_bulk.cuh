@@ -3,9 +3,10 @@
 // loads and stores: one elected thread keeps several tiles of p/g/m/v in flight
 // per SM, the other threads only touch shared memory.
 //
-// Only full, 16-byte aligned FP16 work items take this route; everything else in
-// the table (ragged tails, FP32 tensors, statistics-only entries) is handled by
-// the direct code of adamw_update.cuh inside the same kernel.
+// Only full, 16-byte aligned FP16 work items (FP16 or FP32 gradients, with or without
+// a master copy) take this route; everything else in the table (partial items, FP32
+// and bfloat16 tensors, statistics-only entries) is handled by the direct code of
+// adamw_update.cuh inside the same kernel.
 //
 // Waits on the load barriers are bounded: when a wait gives up the CTA records it
 // in the error word, drains its own copies (again bounded) and returns.
@@ -20,7 +21,7 @@ constexpr int kBulkTile = 2048;                       // elements per stage
 constexpr int kBulkTilesPerItem = kChunk / kBulkTile;
 constexpr int kBulkStages = 6;
 constexpr int kBulkDepth = kBulkStages - 2;           // tiles loading ahead of the one in use
-constexpr int kBulkStageBytes = 32768;                // [m 8K][v 8K][master 8K][p 4K][g 4K]
+constexpr int kBulkStageBytes = 36864;                // [m 8K][v 8K][master 8K][p 4K][g 8K: FP16 uses the first 4K]
 constexpr int kBulkSmemBytes = kBulkStages * kBulkStageBytes;
 constexpr uint32_t kBulkWaitTries = 1u << 18;
 constexpr int kBulkPendingCap = 1024;                 // items per CTA remembered for the direct code
@@ -79,7 +80,7 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 __device__ __forceinline__ bool bulk_eligible(const WorkItem& it) {
     const uint32_t kind = it.flags & kItemKindMask;
     return it.count == (uint32_t)kChunk && (it.flags & kItemVec16) && kind != kItemKindF32 &&
-           !(it.flags & (RLCU_TENSOR_NORM_ONLY | kItemBF16 | kItemGradF32));
+           !(it.flags & (RLCU_TENSOR_NORM_ONLY | kItemBF16));
 }
 
 // Issues the loads of one tile into a stage (one thread).
@@ -87,14 +88,15 @@ __device__ __forceinline__ void bulk_issue_tile(const WorkItem& it, int sub, uns
     const size_t e = (size_t)sub * kBulkTile;
     const bool master = (it.flags & kItemKindMask) == kItemKindF16Master;
     const bool zero = (it.flags & RLCU_TENSOR_GRAD_ZERO) != 0;
-    const uint32_t bytes = 2u * kBulkTile * 4u + (master ? kBulkTile * 4u : kBulkTile * 2u) + (zero ? 0u : kBulkTile * 2u);
+    const uint32_t gbytes = (it.flags & kItemGradF32) ? kBulkTile * 4u : kBulkTile * 2u;
+    const uint32_t bytes = 2u * kBulkTile * 4u + (master ? kBulkTile * 4u : kBulkTile * 2u) + (zero ? 0u : gbytes);
     mbar_expect_tx(bar, bytes);
     const uint32_t s = smem_u32(stage);
     bulk_load(s, it.m + e, kBulkTile * 4, bar);
     bulk_load(s + 8192, it.v + e, kBulkTile * 4, bar);
     if (master) bulk_load(s + 16384, it.master + e, kBulkTile * 4, bar);
     else bulk_load(s + 24576, static_cast<const __half*>(it.p) + e, kBulkTile * 2, bar);
-    if (!zero) bulk_load(s + 28672, static_cast<const __half*>(it.g) + e, kBulkTile * 2, bar);
+    if (!zero) bulk_load(s + 28672, static_cast<const char*>(it.g) + e * (gbytes / kBulkTile), gbytes, bar);
 }
 
 // Issues the stores of one finished tile (one thread) and commits them as one group.
@@ -113,8 +115,10 @@ __device__ __forceinline__ void bulk_store_tile(const WorkItem& it, int sub, uns
         const ptrdiff_t off = (static_cast<__half*>(it.p) + e) - peers.local_base;
         for (int j = 0; j < peers.n; j++) bulk_store(peers.base[j] + off, s + 24576, kBulkTile * 2);
     }
-    if (zero_grads && !(it.flags & RLCU_TENSOR_GRAD_ZERO))
-        bulk_store(const_cast<__half*>(static_cast<const __half*>(it.g)) + e, s + 28672, kBulkTile * 2);
+    if (zero_grads && !(it.flags & RLCU_TENSOR_GRAD_ZERO)) {
+        const uint32_t gbytes = (it.flags & kItemGradF32) ? kBulkTile * 4u : kBulkTile * 2u;
+        bulk_store(const_cast<char*>(static_cast<const char*>(it.g)) + e * (gbytes / kBulkTile), s + 28672, gbytes);
+    }
     bulk_commit();
 }
 
@@ -123,6 +127,7 @@ __device__ __forceinline__ void bulk_compute_tile(const WorkItem& it, unsigned c
                                                   const GradXform& xf) {
     const bool master = (it.flags & kItemKindMask) == kItemKindF16Master;
     const bool zero = (it.flags & RLCU_TENSOR_GRAD_ZERO) != 0;
+    const bool gf32 = (it.flags & kItemGradF32) != 0;
     const float decay = decay_factor(c.lr, it.wd);
     const int t = threadIdx.x;
     float4* sm = reinterpret_cast<float4*>(stage) + t;
@@ -141,8 +146,12 @@ __device__ __forceinline__ void bulk_compute_tile(const WorkItem& it, unsigned c
         const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&x.y));
         w[0] = a.x; w[1] = a.y; w[2] = b.x; w[3] = b.y;
     }
+    float4* sg32 = reinterpret_cast<float4*>(stage + 28672) + t;
     if (zero) {
         g[0] = g[1] = g[2] = g[3] = 0.0f;
+    } else if (gf32) {
+        const float4 x = *sg32;
+        g[0] = x.x; g[1] = x.y; g[2] = x.z; g[3] = x.w;
     } else {
         const uint2 x = *sg;
         const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&x.x));
@@ -153,7 +162,7 @@ __device__ __forceinline__ void bulk_compute_tile(const WorkItem& it, unsigned c
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         float x = __fmul_rn(g[i], xf.coef);
-        if (xf.round_half) x = round_through_half(x);
+        if (xf.round_half && !gf32) x = round_through_half(x);     // FP32 gradients are scaled in FP32 (trainer.h:144)
         w[i] = adamw_element(w[i], x, mm[i], vv[i], c, decay);
     }
     *sm = make_float4(mm[0], mm[1], mm[2], mm[3]);
@@ -164,7 +173,10 @@ __device__ __forceinline__ void bulk_compute_tile(const WorkItem& it, unsigned c
     out.x = *reinterpret_cast<uint32_t*>(&lo);
     out.y = *reinterpret_cast<uint32_t*>(&hi);
     *sp = out;
-    if (xf.zero_grads && !zero) *sg = make_uint2(0u, 0u);
+    if (xf.zero_grads && !zero) {
+        if (gf32) *sg32 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        else *sg = make_uint2(0u, 0u);
+    }
 }
 
 // Body of the bulk-copy update kernels (launch: kBulkThreads + 32 threads, one CTA per SM,
@@ -304,12 +316,12 @@ __device__ __forceinline__ void bulk_table_body(const Items items, uint32_t n_it
     asm volatile("bar.sync 1, %0;" :: "n"(kBulkThreads) : "memory");
     if (!ok || threadIdx.x >= kThreads) return;      // the direct code is written for kThreads threads
     const uint32_t listed = n_pending < (uint32_t)kBulkPendingCap ? n_pending : (uint32_t)kBulkPendingCap;
-    for (uint32_t i = 0; i < listed; i++) process_item<PEERS>(items.get(pending[i]), c, xf, peers);
+    for (uint32_t i = 0; i < listed; i++) process_item<PEERS, true>(items.get(pending[i]), c, xf, peers);
     if (n_pending > listed) {
         // more than the list holds: walk the rest of this CTA's items again
         for (uint32_t idx = pending[listed - 1] + gridDim.x; idx < n_items; idx += gridDim.x) {
             const WorkItem it = items.get(idx);
-            if (!bulk_eligible(it)) process_item<PEERS>(it, c, xf, peers);
+            if (!bulk_eligible(it)) process_item<PEERS, true>(it, c, xf, peers);
         }
     }
 }

@@ -636,7 +636,8 @@ int rlcu_tensor_list_create(const rlcu_tensor_desc* descs, uint64_t count, rlcu_
         const size_t esz = d.dtype == RLCU_F32 ? 4 : 2;
         const size_t gesz = grad_elem_size(d);
         if (bits & kItemGradF32) any_grad_f32 = true;
-        if (!(d.flags & RLCU_TENSOR_NORM_ONLY) && d.master && d.dtype == RLCU_F16 && !(bits & kItemGradF32)) master_numel += d.n;
+        // streams per element beyond the five of the plain FP16 update: a master copy, an FP32 gradient
+        if (!(d.flags & RLCU_TENSOR_NORM_ONLY) && d.dtype == RLCU_F16 && (d.master || (bits & kItemGradF32))) master_numel += d.n;
         // Work items are cut so that, from the second one on, every pointer sits on a
         // common grid in every stream: a tensor that starts off it (ragged sizes packed into
         // one arena) gets a partial head item first (see grid_head)
@@ -669,7 +670,7 @@ int rlcu_tensor_list_create(const rlcu_tensor_desc* descs, uint64_t count, rlcu_
     L->has_grad_f32 = any_grad_f32;
     // lists that are mostly FP16 weights with FP32 masters run faster through the bulk-copy
     // kernel (see launch_flat); the others through the direct one
-    L->prefer_bulk = !any_grad_f32 && master_numel * 2 > numel && items.size() >= 4ull * (uint64_t)di.sms;
+    L->prefer_bulk = master_numel * 2 > numel && items.size() >= 4ull * (uint64_t)di.sms;
     const uint64_t cap_u = (uint64_t)di.sms * (any_grad_f32 ? di.occ_table_gf32 : di.occ_table), cap_s = (uint64_t)di.sms * di.occ_stat;
     L->grid_update = (int)(L->n_items < cap_u ? (L->n_items ? L->n_items : 1) : cap_u);
     L->grid_stat = (int)(L->n_items < cap_s ? (L->n_items ? L->n_items : 1) : cap_s);
@@ -780,8 +781,6 @@ int rlcu_adamw_multi_step(rlcu_tensor_list* list, const rlcu_hparams* hp,
     if (!(step_flags & RLCU_STEP_DIRECT) && list->prefer_bulk && !direct_only()) step_flags |= RLCU_STEP_BULK_COPY;
     step_flags &= ~(uint32_t)RLCU_STEP_DIRECT;
     if (step_flags & RLCU_STEP_BULK_COPY) {
-        if (list->has_grad_f32)
-            return set_error(RLCU_ERR_UNSUPPORTED, "the bulk-copy update does not take FP32 gradients for 16-bit parameters");
         DeviceInfo di;
         const int rc = device_info(&di);
         if (rc) return rc;

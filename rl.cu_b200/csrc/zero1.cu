@@ -12,6 +12,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -432,6 +433,18 @@ int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float 
     zero.b = reinterpret_cast<uint4*>(static_cast<char*>(z->grad_pool) + shard_hi);
     zero.b_vecs = (total_bytes - shard_hi) / 16;
     if (z->mode == RLCU_ZERO1_P2P) {
+        if ((step_flags & RLCU_STEP_BULK_COPY) && (step_flags & RLCU_STEP_DIRECT))
+            return set_error(RLCU_ERR_INVALID, "RLCU_STEP_BULK_COPY and RLCU_STEP_DIRECT exclude each other");
+        // Which pair of exchange kernels: with FP16 pools on more than one rank the bulk-copy pair
+        // is the default (1-2 % faster over NVLink at 2 and at 8 ranks); bfloat16 pools and a single
+        // rank keep the per-thread pair.  The flags force either.
+        static const bool env_direct = [] {
+            const char* e = getenv("RLCU_DIRECT_ONLY");
+            return e && e[0] && e[0] != '0';
+        }();
+        const bool bulk = (step_flags & RLCU_STEP_BULK_COPY) ||
+                          (!(step_flags & RLCU_STEP_DIRECT) && !env_direct && z->world > 1 && z->wire_type == ncclHalf);
+        if (bulk) step_flags |= RLCU_STEP_BULK_COPY;
         if (phases & 1u) {
             rlcu::NvtxRange range("rlcu zero1: reduce-scatter + statistics (peer loads)");
             // every rank's gradients are complete before anyone reads them remotely

@@ -423,10 +423,11 @@ reduce_stat_bulk_kernel(const WorkItem* __restrict__ table, uint32_t n_items,
 }
 
 // Clears share `part` of `parts` of the gradient pool outside the shard (RLCU_STEP_ZERO_GRADS).
-__device__ __forceinline__ void zero_slice(const ZeroSpan& z, uint64_t part, uint64_t parts) {
+// `threads` = how many threads of the CTA (the first ones) take part.
+__device__ __forceinline__ void zero_slice(const ZeroSpan& z, uint64_t part, uint64_t parts, uint32_t threads) {
     const uint64_t total = z.a_vecs + z.b_vecs;
     const uint64_t lo = total * part / parts, hi = total * (part + 1) / parts;
-    for (uint64_t i = lo + threadIdx.x; i < hi; i += blockDim.x)
+    for (uint64_t i = lo + threadIdx.x; i < hi; i += threads)
         __stcs(i < z.a_vecs ? z.a + i : z.b + (i - z.a_vecs), make_uint4(0u, 0u, 0u, 0u));
 }
 
@@ -441,7 +442,7 @@ adamw_table_peer_kernel(const WorkItem* __restrict__ table, uint32_t n_items, St
     if (!resolve_step(stat, step_flags, c, xf)) {
         if (!clear) return;
         clear_gradients(table, n_items);
-        zero_slice(zero, blockIdx.x, gridDim.x);
+        zero_slice(zero, blockIdx.x, gridDim.x, kThreads);
         return;
     }
     uint32_t idx = blockIdx.x;
@@ -452,7 +453,7 @@ adamw_table_peer_kernel(const WorkItem* __restrict__ table, uint32_t n_items, St
         const uint32_t nidx = idx + gridDim.x;
         if (nidx < n_items) next = load_item(table, nidx);
         process_item<true>(it, c, xf, peers);
-        if (clear) zero_slice(zero, idx, n_items);      // spread over the items: rides under the NVLink stores
+        if (clear) zero_slice(zero, idx, n_items, kThreads);      // spread over the items: rides under the NVLink stores
         if (nidx >= n_items) break;
         idx = nidx;
     }
@@ -468,7 +469,7 @@ adamw_table_bulk_peer_kernel(const WorkItem* __restrict__ table, uint32_t n_item
     bulk_table_body<true>(TableItems{table}, n_items, c, stat, step_flags, error_word, peers);
     // the rest of the gradient pool (RLCU_STEP_ZERO_GRADS): by the consumer threads, after
     // their tiles; the shard's own gradients were cleared tile by tile
-    if ((step_flags & RLCU_STEP_ZERO_GRADS) && threadIdx.x < kBulkThreads) zero_slice(zero, blockIdx.x, gridDim.x);
+    if ((step_flags & RLCU_STEP_ZERO_GRADS) && threadIdx.x < kBulkThreads) zero_slice(zero, blockIdx.x, gridDim.x, kBulkThreads);
 }
 
 struct Geometry {

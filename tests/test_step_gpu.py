@@ -525,11 +525,13 @@ def test_bulk_copy_update_equals_the_direct_update(pkg, O, torch, extra):
              (3000, "f", 0.0, pkg.TENSOR_NORM_ONLY)]
     flags = pkg.STEP_ROUND_CLIP_FP16 | (pkg.STEP_ZERO_GRADS if extra else 0)
     results = []
+    stat = None
     for bulk in (0, pkg.STEP_BULK_COPY):
         host, dev, descs = make_case(O, torch, pkg, specs, seed=81)
         tl = pkg.TensorList(descs)
-        stat = torch.zeros(16, device="cuda")
-        tl.gradstat(stat.data_ptr(), 1.0, 1.0)
+        if stat is None:                 # one record for both runs (the sum's order depends on addresses)
+            stat = torch.zeros(16, device="cuda")
+            tl.gradstat(stat.data_ptr(), 1.0, 1.0)
         for t in (2, 3, 4):
             tl.step(pkg.hparams(1e-4, 0.9, 0.999, 1e-8, t), stat.data_ptr(), flags | bulk)
         tl.check()
@@ -546,12 +548,14 @@ def test_master_lists_default_to_the_bulk_copy_kernel_with_the_same_bits(pkg, O,
     of the oracle."""
     specs = [(8192 * 400 + 11, "hm", 0.01, 0), (8192 * 300, "hm", 0.0, 0), (5000, "f", 0.0, 0), (8192 * 20 + 3, "h", 0.01, 0)]
     results = []
+    stat = None
     for forced in (0, pkg.STEP_DIRECT):
         host, dev, descs = make_case(O, torch, pkg, specs, seed=171)
         tl = pkg.TensorList(descs)
-        stat = torch.zeros(16, device="cuda")
         hp = pkg.hparams(1e-4, 0.9, 0.999, 1e-8, 3)
-        tl.gradstat(stat.data_ptr(), 1.0, 1.0)
+        if stat is None:                 # one record for both runs (the sum's order depends on addresses)
+            stat = torch.zeros(16, device="cuda")
+            tl.gradstat(stat.data_ptr(), 1.0, 1.0)
         tl.step(hp, stat.data_ptr(), pkg.STEP_ROUND_CLIP_FP16 | forced)
         tl.check()
         got = read_stat(pkg, stat)
@@ -736,12 +740,32 @@ def test_fp32_gradients_zeroed_after_the_update_and_on_a_skipped_step(pkg, O, to
     assert not dev[0]["g"].get().any() and not dev[1]["g"].get().any()
 
 
-def test_bulk_copy_update_refuses_fp32_gradient_lists(pkg, O, torch):
-    _, dev, descs = make_case(O, torch, pkg, [(8192, "hg", 0.0, 0)], seed=141)
-    tl = pkg.TensorList(descs)
-    with pytest.raises(pkg.RlcuError) as e:
-        tl.step(pkg.hparams(1e-4, 0.9, 0.999, 1e-8, 1), None, pkg.STEP_BULK_COPY)
-    assert e.value.code == pkg.ERR_UNSUPPORTED
+@pytest.mark.parametrize("zero_grads", [False, True])
+def test_bulk_copy_update_takes_fp32_gradients(pkg, O, torch, zero_grads):
+    """FP32 gradients for FP16 parameters through the bulk-copy kernel: the bits of the direct kernel."""
+    specs = [(8192 * 5 + 9, "hg", 0.01, 0), (8192 * 3, "hmg", 0.0, 0), (8192 * 2, "hm", 0.01, 0), (777, "hg", 0.0, 0),
+             (8192 * 4, "hmg", 0.0, pkg.TENSOR_GRAD_ZERO)]
+    flags = pkg.STEP_ROUND_CLIP_FP16 | (pkg.STEP_ZERO_GRADS if zero_grads else 0)
+    results = []
+    stat = None
+    for how in (pkg.STEP_DIRECT, pkg.STEP_BULK_COPY):
+        host, dev, descs = make_case(O, torch, pkg, specs, seed=141)
+        tl = pkg.TensorList(descs)
+        if stat is None:
+            # one record for both runs: work items are cut by address, so the squares of two
+            # copies of the same data at other addresses are added in another order
+            stat = torch.zeros(16, device="cuda")
+            tl.gradstat(stat.data_ptr(), 1.0, 1.0)
+        for t in (2, 3):
+            tl.step(pkg.hparams(1e-4, 0.9, 0.999, 1e-8, t), stat.data_ptr(), flags | how)
+        tl.check()
+        results.append([{k: b.get() for k, b in d.items()} for d in dev])
+        assert all(b.guards_intact() for d in dev for b in d.values())
+    for a, b in zip(*results):
+        for k in a:
+            assert np.array_equal(a[k].view(np.uint8), b[k].view(np.uint8)), k
+    if zero_grads:
+        assert not results[1][0]["g"].any() and not results[1][1]["g"].any() and results[1][4]["g"].any()
 
 
 # ---------------------------------------------------------------------------------------------

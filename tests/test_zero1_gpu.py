@@ -462,8 +462,8 @@ def test_create_fails_on_every_rank_when_one_rank_cannot_set_up(pkg, tmp_path):
     assert "32-byte aligned" in m1
 
 
-def _flags_worker(rank, world, port, out_dir, mode, extra_flags):
-    """The same step twice, without and with `extra_flags`, each on fresh buffers."""
+def _flags_worker(rank, world, port, out_dir, mode, extra_flags, plain_flags=0):
+    """The same step twice, with `plain_flags` and with `extra_flags`, each on fresh buffers."""
     import sys
     import torch
     import torch.distributed as dist
@@ -475,7 +475,7 @@ def _flags_worker(rank, world, port, out_dir, mode, extra_flags):
     pkg = entry.load_package()
     torch.cuda.set_device(rank)
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
-    for tag, fl in (("plain", 0), ("flagged", extra_flags)):
+    for tag, fl in (("plain", plain_flags), ("flagged", extra_flags)):
         box = [pkg.zero1_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         out = _run_rank(rank, world, box[0], pkg, O, torch, False, mode, False, fl)
@@ -526,17 +526,19 @@ def test_sharded_step_clears_the_whole_gradient_pool_when_asked(pkg, O, tmp_path
 
 @pytest.mark.parametrize("world", [1, 2])
 def test_sharded_step_through_the_bulk_copy_engine(pkg, O, tmp_path, world):
-    """RLCU_STEP_BULK_COPY in peer-to-peer mode: the peers' gradients are fetched, and the update's
-    traffic (the copies into the peers' pools included) is issued, by cp.async.bulk.  Reduced
-    gradients are bit-identical to the direct kernels'; the sum of squares is taken in another
-    order."""
+    """The two pairs of exchange kernels of peer-to-peer mode against each other: RLCU_STEP_DIRECT
+    (per-thread loads and stores) and RLCU_STEP_BULK_COPY (the peers' gradients fetched, and the
+    update's traffic with the copies into the peers' pools issued, by cp.async.bulk; the default
+    for FP16 pools on several ranks).  Reduced gradients are bit-identical; the sum of squares
+    is taken in another order."""
     import torch
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-    mp.spawn(_flags_worker, args=(world, _free_port(), str(tmp_path), 1, pkg.STEP_BULK_COPY), nprocs=world, join=True)
+    mp.spawn(_flags_worker, args=(world, _free_port(), str(tmp_path), 1, pkg.STEP_BULK_COPY, pkg.STEP_DIRECT),
+             nprocs=world, join=True)
     _compare_flag_runs(pkg, tmp_path, world, grads_cleared=False, same_sum_order=False)
-    mp.spawn(_flags_worker, args=(world, _free_port(), str(tmp_path), 1, pkg.STEP_BULK_COPY | pkg.STEP_ZERO_GRADS),
+    mp.spawn(_flags_worker, args=(world, _free_port(), str(tmp_path), 1, pkg.STEP_BULK_COPY | pkg.STEP_ZERO_GRADS, pkg.STEP_DIRECT),
              nprocs=world, join=True)
     _compare_flag_runs(pkg, tmp_path, world, grads_cleared=True, same_sum_order=False)

@@ -113,6 +113,29 @@ def test_two_pools_of_one_step_combine_into_one_record(pkg, torch):
     assert read_stat(pkg, stat).found_inf == 1
 
 
+def test_second_device_in_the_same_process_has_its_own_scratch(pkg, torch):
+    """The scratch address is resolved once per device (with that device current): calls on two
+    devices of one process each use their own copy of the array and give their own results."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    results = []
+    try:
+        for dev in (0, 1, 0):
+            torch.cuda.set_device(dev)
+            gen = torch.Generator(device=f"cuda:{dev}").manual_seed(10 + dev)
+            g = (torch.randn(1_000_003, device=f"cuda:{dev}", generator=gen) * 1e-2).half()
+            stat = torch.full((16,), 7.0, device=f"cuda:{dev}")
+            pkg.gradstat_flat_noalloc(g.data_ptr(), pkg.F16, g.numel(), stat.data_ptr(), 1.0, 1.0)
+            torch.cuda.synchronize(dev)
+            got = read_stat(pkg, stat)
+            exact = float(torch.sqrt((g.double() ** 2).sum()))
+            assert abs(got.norm - exact) <= NORM_BAR * exact and got.found_inf == 0
+            results.append(got.norm)
+    finally:
+        torch.cuda.set_device(0)
+    assert results[0] == results[2] and results[0] != results[1]
+
+
 def test_sizes_beyond_the_fixed_scratch_are_refused(pkg, torch):
     g = torch.zeros(16, device="cuda").half()
     stat = torch.zeros(16, device="cuda")
