@@ -324,19 +324,23 @@ gradstat_kernel(const WorkItem* __restrict__ table, uint32_t n_items, float unsc
     __syncthreads();
     if (!is_last) return;
 
-    // last CTA to arrive: add the per-CTA partials in index order, in FP64
+    // last CTA to arrive: add the per-CTA partials in FP64, in a fixed order (every thread a
+    // strided few, so that the loads are independent; then the warp tree; then the warps in order)
     __threadfence();
-    if (threadIdx.x < 32) {
-        double s = 0.0;
-        for (uint32_t i = threadIdx.x; i < gridDim.x; i += 32)
-            s += (double)__ldcg(partials + i);
+    __shared__ double warp_totals[kThreads / 32];
+    double s = 0.0;
+    for (uint32_t i = threadIdx.x; i < gridDim.x; i += kThreads) s += (double)__ldcg(partials + i);
 #pragma unroll
-        for (int mask = 16; mask >= 1; mask >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, mask);
-        if (threadIdx.x == 0) {
-            *counter = 0;
-            if (flags & RLCU_STAT_PARTIAL) out->sum_sq = s;
-            else finalize_stat(out, s, unscale, max_norm, scaler);
-        }
+    for (int mask = 16; mask >= 1; mask >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, mask);
+    if ((threadIdx.x & 31) == 0) warp_totals[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double total = 0.0;
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; w++) total += warp_totals[w];
+        *counter = 0;
+        if (flags & RLCU_STAT_PARTIAL) out->sum_sq = total;
+        else finalize_stat(out, total, unscale, max_norm, scaler);
     }
 }
 
@@ -390,6 +394,10 @@ int device_info(DeviceInfo* out) {
         di.flat_error = static_cast<unsigned int*>(word);
         if (di.occ_table < 1 || di.occ_table_gf32 < 1 || di.occ_flat < 1 || di.occ_stat < 1)
             return set_error(RLCU_ERR_CUDA, "kernel does not fit on an SM");
+        if (const char* e = getenv("RLCU_STAT_CTAS_PER_SM")) {      // measurement knob
+            const int cap = atoi(e);
+            if (cap >= 1 && cap < di.occ_stat) di.occ_stat = cap;
+        }
         cache[dev] = di;
         have[dev] = true;
     }
