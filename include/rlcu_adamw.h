@@ -327,6 +327,10 @@ enum {
 };
 /* OR this into `mode` when the two pools hold bfloat16 instead of FP16 */
 #define RLCU_ZERO1_POOLS_BF16 0x100u
+/* OR this into `mode` when the GRADIENT pool holds FP32 (padded_elems floats) for the 16-bit
+ * parameters: gradients are summed in FP32 in rank order and never rounded to 16 bits; twice the
+ * bytes cross NVLink in the reduce-scatter.  See RLCU_GRAD_F32. */
+#define RLCU_ZERO1_GRADS_F32 0x200u
 int rlcu_zero1_make_plan(const rlcu_zero1_segment* segs, uint64_t nsegs, int rank, int world,
                          rlcu_zero1_plan* out);
 /* The descriptors rank `rank` would update, with pointers expressed as element

@@ -42,6 +42,7 @@ UNIQUE_ID_BYTES = 128
 PHASE_REDUCE_SCATTER, PHASE_STATISTICS, PHASE_UPDATE, PHASE_ALL_GATHER = 1, 2, 4, 8
 ZERO1_NCCL, ZERO1_P2P = 0, 1
 ZERO1_POOLS_BF16 = 0x100
+ZERO1_GRADS_F32 = 0x200
 NOALLOC_MAX_ELEMS = 1 << 31
 # C++-linkage launchers with RL.cu's signatures (include/kernels/adamw.cuh)
 CXX_EXPORTS = [

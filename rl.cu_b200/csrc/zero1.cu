@@ -127,7 +127,8 @@ struct rlcu_zero1 {
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1;
     uint32_t mode = RLCU_ZERO1_NCCL;
-    ncclDataType_t wire_type = ncclHalf;   // element type of the pools on the wire (NCCL mode)
+    ncclDataType_t wire_type = ncclHalf;   // element type of the parameter pool on the wire (NCCL mode)
+    bool grads_f32 = false;                // the gradient pool holds FP32 (RLCU_ZERO1_GRADS_F32)
     rlcu_zero1_plan plan{};
     void* param_pool = nullptr;
     void* grad_pool = nullptr;
@@ -334,7 +335,8 @@ int rlcu_zero1_create(const void* unique_id, int rank, int world,
                       uint32_t mode, rlcu_zero1** out) {
     if (!out) return set_error(RLCU_ERR_INVALID, "null out");
     const bool bf16 = (mode & RLCU_ZERO1_POOLS_BF16) != 0;
-    mode &= ~(uint32_t)RLCU_ZERO1_POOLS_BF16;
+    const bool grads_f32 = (mode & RLCU_ZERO1_GRADS_F32) != 0;
+    mode &= ~(uint32_t)(RLCU_ZERO1_POOLS_BF16 | RLCU_ZERO1_GRADS_F32);
     if (mode != RLCU_ZERO1_NCCL && mode != RLCU_ZERO1_P2P) return set_error(RLCU_ERR_INVALID, "unknown mode %u", mode);
     *out = nullptr;
     if (!unique_id || !param_pool || !grad_pool || !m_shard || !v_shard)
@@ -352,6 +354,7 @@ int rlcu_zero1_create(const void* unique_id, int rank, int world,
     z->world = world;
     z->mode = mode;
     z->wire_type = bf16 ? ncclBfloat16 : ncclHalf;
+    z->grads_f32 = grads_f32;
     z->param_pool = param_pool;
     z->grad_pool = grad_pool;
     std::vector<Piece> pieces;
@@ -361,7 +364,8 @@ int rlcu_zero1_create(const void* unique_id, int rank, int world,
     for (const Piece& p : pieces) {
         rlcu_tensor_desc d{};
         d.param = static_cast<char*>(param_pool) + p.pool_offset * 2;
-        d.grad = static_cast<const char*>(grad_pool) + p.pool_offset * 2;
+        d.grad = static_cast<const char*>(grad_pool) + p.pool_offset * (grads_f32 ? 4 : 2);
+        d.grad_dtype = grads_f32 ? RLCU_GRAD_F32 : RLCU_GRAD_AS_PARAM;
         d.m = m_shard + p.state_offset;
         d.v = v_shard + p.state_offset;
         d.master = master_shard ? master_shard + p.state_offset : nullptr;
@@ -410,9 +414,11 @@ int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float 
                     uint32_t phases, void* stream) {
     if (!z || !hp || !stat) return set_error(RLCU_ERR_INVALID, "null argument");
     if (phases == 0) phases = 15;
+    const uint32_t step_flags_in = step_flags;      // as the caller gave them
     cudaStream_t s = (cudaStream_t)stream;
     const uint64_t S = z->plan.shard_elems;
-    char* gshard = static_cast<char*>(z->grad_pool) + (uint64_t)z->rank * S * 2;
+    const uint64_t gsz = z->grads_f32 ? 4 : 2;         // bytes per gradient element
+    char* gshard = static_cast<char*>(z->grad_pool) + (uint64_t)z->rank * S * gsz;
     char* pshard = static_cast<char*>(z->param_pool) + (uint64_t)z->rank * S * 2;
     // gradients are summed, not averaged, on the wire (FP16 would lose the small
     // ones to the division); 1/world goes into the factor applied in registers
@@ -426,7 +432,7 @@ int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float 
         return set_error(RLCU_ERR_INVALID, "device bias correction needs a scaler state");
     // RLCU_STEP_ZERO_GRADS clears the WHOLE local gradient pool: the shard inside the update
     // kernel (each gradient after it was read), the rest beside it.
-    const uint64_t total_bytes = z->plan.padded_elems * 2, shard_lo = (uint64_t)z->rank * S * 2, shard_hi = shard_lo + S * 2;
+    const uint64_t total_bytes = z->plan.padded_elems * gsz, shard_lo = (uint64_t)z->rank * S * gsz, shard_hi = shard_lo + S * gsz;
     rlcu::ZeroSpan zero{};
     zero.a = reinterpret_cast<uint4*>(z->grad_pool);
     zero.a_vecs = shard_lo / 16;
@@ -444,14 +450,21 @@ int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float 
         }();
         const bool bulk = (step_flags & RLCU_STEP_BULK_COPY) ||
                           (!(step_flags & RLCU_STEP_DIRECT) && !env_direct && z->world > 1 && z->wire_type == ncclHalf);
+        // (FP32 gradient pools are always reduced by the per-thread kernel; the flag then only
+        // selects the update kernel)
         if (bulk) step_flags |= RLCU_STEP_BULK_COPY;
         if (phases & 1u) {
             rlcu::NvtxRange range("rlcu zero1: reduce-scatter + statistics (peer loads)");
             // every rank's gradients are complete before anyone reads them remotely
             rc = barrier(z, s);
             if (rc) return rc;
-            rc = rlcu::launch_reduce_stat(z->list, z->grads_in, unscale_all, scaler, stat,
-                                          (step_flags & RLCU_STEP_BULK_COPY) != 0, s);
+            // When the library chooses (no flag given), four ranks keep the per-thread reduce kernel:
+            // its three CTAs per SM with 256-bit loads measured 651 GB/s per direction there against
+            // 636 for the bulk-copy one (at two and at eight ranks the bulk-copy kernel is ahead).
+            const bool bulk_reduce = (step_flags_in & RLCU_STEP_BULK_COPY) || (bulk && z->world != 4);
+            rc = z->grads_f32
+                     ? rlcu::launch_reduce_stat_f32(z->list, z->grads_in, unscale_all, scaler, stat, s)
+                     : rlcu::launch_reduce_stat(z->list, z->grads_in, unscale_all, scaler, stat, bulk_reduce, s);
             if (rc) return rc;
         }
         if (phases & 2u) {
@@ -473,7 +486,8 @@ int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float 
     }
     if (phases & 1u) {
         rlcu::NvtxRange range("rlcu zero1: ncclReduceScatter");
-        RLCU_NCCL(z->api, z->api->ReduceScatter(z->grad_pool, gshard, S, z->wire_type, ncclSum, z->comm, s));
+        RLCU_NCCL(z->api, z->api->ReduceScatter(z->grad_pool, gshard, S, z->grads_f32 ? ncclFloat : z->wire_type,
+                                                ncclSum, z->comm, s));
     }
     if (phases & 2u) {
         rlcu::NvtxRange range("rlcu zero1: statistics + norm all-reduce");

@@ -216,6 +216,119 @@ reduce_stat_kernel(const WorkItem* __restrict__ table, uint32_t n_items,
 }
 
 // ---------------------------------------------------------------------------
+// reduce-scatter + statistics over FP32 gradient pools (RLCU_ZERO1_GRADS_F32)
+// ---------------------------------------------------------------------------
+// For 16-bit parameters whose gradients were accumulated in FP32.  Every element of the shard
+// is loaded from all ranks' pools, added in FP32 in rank order and stored as FP32: unlike the
+// 16-bit wire nothing is rounded, and twice the bytes cross NVLink.
+__global__ void __launch_bounds__(kThreads)
+reduce_stat_f32_kernel(const WorkItem* __restrict__ table, uint32_t n_items,
+                       const __grid_constant__ PeerIn peers, float unscale_arg,
+                       const rlcu_scaler_state* scaler, rlcu_stat* out, float* partials,
+                       unsigned int* counter) {
+    __shared__ float warp_sums[kThreads / 32];
+    __shared__ bool is_last;
+    float unscale = unscale_arg;
+    if (scaler) {
+        const float mul = scaler->grad_mul == 0.0f ? 1.0f : scaler->grad_mul;
+        unscale = __fmul_rn(mul, __fdiv_rn(1.0f, scaler->scale));
+    }
+    const int n = peers.n;
+    const float* local_base = reinterpret_cast<const float*>(peers.local_base);
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float probe = 0.0f;
+    for (uint32_t idx = blockIdx.x; idx < n_items; idx += gridDim.x) {
+        const WorkItem* wi = table + idx;
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(wi));        // p, g
+        const uint4 d = __ldg(reinterpret_cast<const uint4*>(wi) + 2);    // master, count, wd
+        const uint4 e = __ldg(reinterpret_cast<const uint4*>(wi) + 3);    // flags
+        float* g = reinterpret_cast<float*>(((uint64_t)a.w << 32) | a.z);
+        const uint32_t count = d.z;
+        const uint32_t fl = e.x;
+        if (fl & RLCU_TENSOR_GRAD_ZERO) continue;
+        const ptrdiff_t base_off = g - local_base;
+        const uint32_t quads = (fl & kItemVec16) ? count / 4 : 0;
+        // two 16-byte vectors per rank in flight per thread
+        uint32_t q = threadIdx.x;
+        for (; q + kThreads < quads; q += 2 * kThreads) {
+            float4 x0[kMaxWorld], x1[kMaxWorld];
+#pragma unroll
+            for (int j = 0; j < kMaxWorld; j++) {
+                if (j < n) {
+                    const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(peers.base[j]) + base_off);
+                    x0[j] = __ldcs(src + q);
+                    x1[j] = __ldcs(src + q + kThreads);
+                }
+            }
+            float4 s0 = x0[0], s1 = x1[0];
+#pragma unroll
+            for (int j = 1; j < kMaxWorld; j++) {
+                if (j < n) {
+                    s0.x = __fadd_rn(s0.x, x0[j].x); s0.y = __fadd_rn(s0.y, x0[j].y);
+                    s0.z = __fadd_rn(s0.z, x0[j].z); s0.w = __fadd_rn(s0.w, x0[j].w);
+                    s1.x = __fadd_rn(s1.x, x1[j].x); s1.y = __fadd_rn(s1.y, x1[j].y);
+                    s1.z = __fadd_rn(s1.z, x1[j].z); s1.w = __fadd_rn(s1.w, x1[j].w);
+                }
+            }
+            reinterpret_cast<float4*>(g)[q] = s0;
+            reinterpret_cast<float4*>(g)[q + kThreads] = s1;
+            const float v[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                probe = __fmaf_rn(v[k], 0.0f, probe);
+                const float t = v[k] * unscale;
+                acc[k & 3] = fmaf(t, t, acc[k & 3]);
+            }
+        }
+        for (; q < quads; q += kThreads) {
+            float4 s0 = __ldcs(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(peers.base[0]) + base_off) + q);
+            for (int j = 1; j < n; j++) {
+                const float4 x = __ldcs(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(peers.base[j]) + base_off) + q);
+                s0.x = __fadd_rn(s0.x, x.x); s0.y = __fadd_rn(s0.y, x.y);
+                s0.z = __fadd_rn(s0.z, x.z); s0.w = __fadd_rn(s0.w, x.w);
+            }
+            reinterpret_cast<float4*>(g)[q] = s0;
+            const float v[4] = {s0.x, s0.y, s0.z, s0.w};
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                probe = __fmaf_rn(v[k], 0.0f, probe);
+                const float t = v[k] * unscale;
+                acc[k] = fmaf(t, t, acc[k]);
+            }
+        }
+        for (uint32_t i = quads * 4 + threadIdx.x; i < count; i += kThreads) {
+            float sum = reinterpret_cast<const float*>(peers.base[0])[base_off + i];
+            for (int j = 1; j < n; j++) sum = __fadd_rn(sum, reinterpret_cast<const float*>(peers.base[j])[base_off + i]);
+            g[i] = sum;
+            probe = __fmaf_rn(sum, 0.0f, probe);
+            const float t = sum * unscale;
+            acc[0] = fmaf(t, t, acc[0]);
+        }
+    }
+    float mine = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    if (isnan(probe)) mine = __int_as_float(0x7FC00000);
+    const float block_total = block_sum(mine, warp_sums);
+    if (threadIdx.x == 0) {
+        partials[blockIdx.x] = block_total;
+        __threadfence();
+        is_last = (atomicAdd(counter, 1u) == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (threadIdx.x < 32) {
+        double s = 0.0;
+        for (uint32_t i = threadIdx.x; i < gridDim.x; i += 32) s += (double)__ldcg(partials + i);
+#pragma unroll
+        for (int mask = 16; mask >= 1; mask >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, mask);
+        if (threadIdx.x == 0) {
+            *counter = 0;
+            out->sum_sq = s;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
 // reduce-scatter + statistics with the peers' gradients fetched by the bulk-copy engine
 // ---------------------------------------------------------------------------
 // Same result as reduce_stat_kernel, bit for bit in the reduced gradients (FP32 sum in rank
@@ -431,6 +544,7 @@ __device__ __forceinline__ void zero_slice(const ZeroSpan& z, uint64_t part, uin
         __stcs(i < z.a_vecs ? z.a + i : z.b + (i - z.a_vecs), make_uint4(0u, 0u, 0u, 0u));
 }
 
+template <bool GF32>
 __global__ void __launch_bounds__(kThreads)
 adamw_table_peer_kernel(const WorkItem* __restrict__ table, uint32_t n_items, StepConsts c,
                         const rlcu_stat* __restrict__ stat, uint32_t step_flags,
@@ -452,7 +566,7 @@ adamw_table_peer_kernel(const WorkItem* __restrict__ table, uint32_t n_items, St
         const WorkItem it = next;
         const uint32_t nidx = idx + gridDim.x;
         if (nidx < n_items) next = load_item(table, nidx);
-        process_item<true>(it, c, xf, peers);
+        process_item<true, GF32>(it, c, xf, peers);
         if (clear) zero_slice(zero, idx, n_items, kThreads);      // spread over the items: rides under the NVLink stores
         if (nidx >= n_items) break;
         idx = nidx;
@@ -474,6 +588,7 @@ adamw_table_bulk_peer_kernel(const WorkItem* __restrict__ table, uint32_t n_item
 
 struct Geometry {
     int sms = 0, occ_reduce[5] = {0, 0, 0, 0, 0}, occ_update = 0;   // reduce: generic, 1, 2, 4, 8 ranks
+    int occ_update_gf32 = 0, occ_reduce_f32 = 0;
 };
 
 int geometry(Geometry* out) {
@@ -492,14 +607,16 @@ int geometry(Geometry* out) {
         RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&g.occ_reduce[2], reduce_stat_kernel<2>, kThreads, 0));
         RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&g.occ_reduce[3], reduce_stat_kernel<4>, kThreads, 0));
         RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&g.occ_reduce[4], reduce_stat_kernel<8>, kThreads, 0));
-        RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&g.occ_update, adamw_table_peer_kernel, kThreads, 0));
+        RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&g.occ_update, adamw_table_peer_kernel<false>, kThreads, 0));
+        RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&g.occ_update_gf32, adamw_table_peer_kernel<true>, kThreads, 0));
+        RLCU_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&g.occ_reduce_f32, reduce_stat_f32_kernel, kThreads, 0));
         RLCU_CUDA(cudaFuncSetAttribute(adamw_table_bulk_peer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kBulkSmemBytes));
         RLCU_CUDA(cudaFuncSetAttribute(reduce_stat_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kRbSmemBytes));
         for (int occ : g.occ_reduce)
             if (occ < 1) return set_error(RLCU_ERR_CUDA, "kernel does not fit on an SM");
-        if (g.occ_update < 1) return set_error(RLCU_ERR_CUDA, "kernel does not fit on an SM");
+        if (g.occ_update < 1 || g.occ_update_gf32 < 1 || g.occ_reduce_f32 < 1) return set_error(RLCU_ERR_CUDA, "kernel does not fit on an SM");
         // measurement knobs: cap the resident CTAs per SM of the two exchange kernels
         if (const char* e = getenv("RLCU_P2P_REDUCE_CTAS_PER_SM")) {
             const int cap = atoi(e);
@@ -557,6 +674,22 @@ int launch_reduce_stat(rlcu_tensor_list* list, const PeerIn& peers, float unscal
     return RLCU_OK;
 }
 
+int launch_reduce_stat_f32(rlcu_tensor_list* list, const PeerIn& peers, float unscale,
+                           const rlcu_scaler_state* scaler, rlcu_stat* stat, cudaStream_t stream) {
+    if (!list || !stat) return set_error(RLCU_ERR_INVALID, "null list or stat");
+    if (peers.n < 1 || peers.n > kMaxWorld) return set_error(RLCU_ERR_INVALID, "world size %d not supported", peers.n);
+    Geometry g;
+    const int rc = geometry(&g);
+    if (rc) return rc;
+    int grid = g.sms * g.occ_reduce_f32;
+    if (grid > list->grid_stat) grid = list->grid_stat;
+    if ((uint32_t)grid > list->n_items) grid = list->n_items ? (int)list->n_items : 1;
+    reduce_stat_f32_kernel<<<grid, kThreads, 0, stream>>>(list->d_items, list->n_items, peers, unscale, scaler, stat,
+                                                          list->d_partials, list->d_counter);
+    RLCU_CUDA(cudaGetLastError());
+    return RLCU_OK;
+}
+
 int launch_update_peers(rlcu_tensor_list* list, const rlcu_hparams* hp, const rlcu_stat* stat,
                         uint32_t step_flags, const PeerOut& peers, const ZeroSpan& zero, cudaStream_t stream) {
     if (!list || !hp) return set_error(RLCU_ERR_INVALID, "null list or hparams");
@@ -592,8 +725,15 @@ int launch_update_peers(rlcu_tensor_list* list, const rlcu_hparams* hp, const rl
         RLCU_CUDA(cudaGetLastError());
         return RLCU_OK;
     }
-    adamw_table_peer_kernel<<<grid, kThreads, 0, stream>>>(list->d_items, list->n_items, c, stat,
-                                                           step_flags, peers, zero);
+    if (list->has_grad_f32) {
+        grid = g.sms * g.occ_update_gf32;
+        if ((uint32_t)grid > list->n_items) grid = (int)list->n_items;
+        adamw_table_peer_kernel<true><<<grid, kThreads, 0, stream>>>(list->d_items, list->n_items, c, stat,
+                                                                     step_flags, peers, zero);
+    } else {
+        adamw_table_peer_kernel<false><<<grid, kThreads, 0, stream>>>(list->d_items, list->n_items, c, stat,
+                                                                      step_flags, peers, zero);
+    }
     RLCU_CUDA(cudaGetLastError());
     return RLCU_OK;
 }

@@ -20,6 +20,11 @@ struct PeerIn {
     const __half* base[kMaxWorld];
 };
 
+// The same for an FP32 gradient pool (peers.base / local_base then point at floats): FP32 sum in
+// rank order, stored as FP32, nothing rounded.
+int launch_reduce_stat_f32(rlcu_tensor_list* list, const PeerIn& peers, float unscale,
+                           const rlcu_scaler_state* scaler, rlcu_stat* stat, cudaStream_t stream);
+
 // The part of this rank's gradient pool that lies outside its shard, as two runs of 16-byte
 // vectors (before and after the shard).  With RLCU_STEP_ZERO_GRADS the update kernel clears
 // it while it works: once the norm has been all-reduced no other rank reads this pool any

@@ -542,3 +542,115 @@ def test_sharded_step_through_the_bulk_copy_engine(pkg, O, tmp_path, world):
     mp.spawn(_flags_worker, args=(world, _free_port(), str(tmp_path), 1, pkg.STEP_BULK_COPY | pkg.STEP_ZERO_GRADS, pkg.STEP_DIRECT),
              nprocs=world, join=True)
     _compare_flag_runs(pkg, tmp_path, world, grads_cleared=True, same_sum_order=False)
+
+
+# ---------------------------------------------------------------------------------------------
+# FP32 gradient pools (RLCU_ZERO1_GRADS_F32)
+# ---------------------------------------------------------------------------------------------
+
+def _f32_grads(O, world):
+    total, p, m, v, grads = _inputs(O, world)
+    out = []
+    for r, g in enumerate(grads):
+        fine = np.random.default_rng([202, r]).standard_normal(total).astype(np.float32)
+        out.append((O.h2f(g) * (np.float32(1) + np.float32(2.0 ** -13) * fine)).astype(np.float32))
+    return total, p, m, v, out
+
+
+def _f32_worker(rank, world, port, out_dir, mode, use_master):
+    import sys
+    import torch
+    import torch.distributed as dist
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    sys.path.insert(0, os.path.join(root, "tests"))
+    import __graft_entry__ as entry
+    from oracle import oracle as O
+    pkg = entry.load_package()
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    box = [pkg.zero1_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    total, p, m, v, grads = _f32_grads(O, world)
+    plan = pkg.zero1_plan(SEGS, rank, world)
+    S, padded = int(plan.shard_elems), int(plan.padded_elems)
+    lo = rank * S
+
+    def padded_of(a, dtype):
+        out = np.zeros(padded, dtype)
+        out[:total] = a
+        return out
+
+    p_pool = torch.from_numpy(padded_of(p, np.uint16).view(np.int16)).cuda()
+    g_pool = torch.from_numpy(padded_of(grads[rank], np.float32)).cuda()
+    m_sh = torch.from_numpy(padded_of(m, np.float32)[lo:lo + S].copy()).cuda()
+    v_sh = torch.from_numpy(padded_of(v, np.float32)[lo:lo + S].copy()).cuda()
+    master_sh = torch.from_numpy(padded_of(O.h2f(p), np.float32)[lo:lo + S].copy()).cuda() if use_master else None
+    stat = torch.zeros(16, device="cuda")
+    z = pkg.Zero1(box[0], rank, world, p_pool.data_ptr(), g_pool.data_ptr(), SEGS, m_sh.data_ptr(), v_sh.data_ptr(),
+                  master_sh.data_ptr() if use_master else None, mode=mode | pkg.ZERO1_GRADS_F32)
+    z.step(pkg.hparams(LR, B1, B2, EPS, T), stat.data_ptr(), 1.0, MAX_NORM, None, pkg.STEP_ROUND_CLIP_FP16)
+    torch.cuda.synchronize()
+    z.poll_error()
+    out = dict(p=p_pool.cpu().numpy().view(np.uint16), g=g_pool.cpu().numpy(), m=m_sh.cpu().numpy(), v=v_sh.cpu().numpy(),
+               stat=stat.cpu().numpy(), lo=lo, S=S)
+    if use_master:
+        out["master"] = master_sh.cpu().numpy()
+    z.close()
+    np.savez(os.path.join(out_dir, f"f32rank{rank}.npz"), **out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", [0, 1], ids=["nccl", "p2p"])
+@pytest.mark.parametrize("world,use_master", [(1, False), (2, True), (4, False)])
+def test_sharded_step_with_fp32_gradient_pools(pkg, O, tmp_path, world, use_master, mode):
+    """FP16 parameters whose gradients arrive in FP32 (RL.cu accumulates dW in FP16,
+    src/kernels/linear.cu:85-98; this is the variant for a caller that accumulates in FP32):
+    the reduce-scatter adds in FP32 and rounds nothing, and the sharded update equals the
+    oracle's step with FP32 gradients on the summed gradients, bit for bit."""
+    import torch
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    mp.spawn(_f32_worker, args=(world, _free_port(), str(tmp_path), mode, use_master), nprocs=world, join=True)
+    outs = []
+    for r in range(world):
+        zf = np.load(tmp_path / f"f32rank{r}.npz")
+        outs.append({k: (zf[k] if zf[k].ndim else zf[k].item()) for k in zf.files})
+    total, p, m, v, grads = _f32_grads(O, world)
+    S = outs[0]["S"]
+    acc = grads[0].copy()
+    for g in grads[1:]:
+        acc = (acc + g).astype(np.float32)            # FP32 adds in rank order
+    g_sum = np.zeros(total, np.float32)
+    for o in outs:
+        lo, hi = o["lo"], min(o["lo"] + S, total)
+        g_sum[lo:hi] = o["g"][lo:hi]
+    if mode == 1 or world <= 2:
+        assert np.array_equal(g_sum.view(np.uint32), acc.view(np.uint32)), "reduced gradients are not the rank-order FP32 sum"
+    else:
+        assert np.all(np.abs(g_sum - acc) <= 4e-7 * np.sum([np.abs(g) for g in grads], axis=0) + 1e-30)
+    master = O.h2f(p)
+    entries, off = [], 0
+    for n, wd, fl in SEGS:
+        e = dict(p=p[off:off + n], g=g_sum[off:off + n], m=m[off:off + n], v=v[off:off + n], wd=wd, flags=fl,
+                 dtype=O.F16, grad_dtype=O.GRAD_F32)
+        if use_master:
+            e["master"] = master[off:off + n]
+        entries.append(e)
+        off += n
+    ts = O.make_tensors(entries)
+    want = O.gradstat(ts, 1.0 / world, MAX_NORM)
+    got = pkg.Stat.from_buffer_copy(outs[0]["stat"].tobytes())
+    assert got.found_inf == 0 and got.clip_active == want.clip_active == 1
+    assert abs(got.norm - want.norm) <= 1e-5 * want.norm
+    O.multi_step(ts, O.HParams(LR, B1, B2, EPS, O.bias_correction(B1, T), O.bias_correction(B2, T)),
+                 O.gradstat_finalize(got.sum_sq, 0, 1.0 / world, MAX_NORM), O.STEP_ROUND_CLIP_FP16)
+    for r, o in enumerate(outs):
+        assert np.array_equal(o["p"][:total], p), f"rank {r}: parameters after all-gather differ"
+        lo, hi = o["lo"], min(o["lo"] + S, total)
+        assert np.array_equal(o["m"][:hi - lo], m[lo:hi]) and np.array_equal(o["v"][:hi - lo], v[lo:hi])
+        if use_master:
+            assert np.array_equal(o["master"][:hi - lo], master[lo:hi])
