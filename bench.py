@@ -779,7 +779,7 @@ def run_sharded(args):
     K = args.steps
     with ClockSampler(local) as clocks:
         ms_per_step = timed(0, K)
-    z.poll_error()
+    z.check()
     final = pkg.Stat.from_buffer_copy(stat.cpu().numpy().tobytes())
     ks = max(3, min(K, 10))
     if mode == pkg.ZERO1_P2P:

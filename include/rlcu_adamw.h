@@ -372,6 +372,10 @@ int rlcu_zero1_step(rlcu_zero1* z, const rlcu_hparams* hp, float unscale, float 
 /* Reports an asynchronous NCCL failure (a peer that died, a timed-out
  * collective) without blocking: RLCU_OK or RLCU_ERR_NCCL. */
 int rlcu_zero1_poll_error(rlcu_zero1* z);
+/* Blocking check after one or more steps: waits for the device, then reports a bounded wait
+ * of the bulk-copy exchange kernels that gave up (RLCU_ERR_TIMEOUT: that step is incomplete) or
+ * an asynchronous NCCL failure. */
+int rlcu_zero1_check(rlcu_zero1* z);
 /* Tears the communicator down; `abort` != 0 uses ncclCommAbort (after a failure). */
 int rlcu_zero1_destroy(rlcu_zero1* z, int abort);
 

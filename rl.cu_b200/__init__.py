@@ -35,7 +35,7 @@ EXPORTS = [
     "rlcu_tensor_list_work_items", "rlcu_gradstat", "rlcu_gradstat_finalize",
     "rlcu_adamw_multi_step", "rlcu_bias_correction", "rlcu_gradstat_flat_noalloc",
     "rlcu_zero1_make_plan", "rlcu_zero1_plan_pieces", "rlcu_zero1_unique_id", "rlcu_zero1_create",
-    "rlcu_zero1_step", "rlcu_zero1_poll_error", "rlcu_zero1_destroy",
+    "rlcu_zero1_step", "rlcu_zero1_poll_error", "rlcu_zero1_check", "rlcu_zero1_destroy",
     "rlcu_checkpoint_save", "rlcu_checkpoint_peek", "rlcu_checkpoint_load",
 ]
 UNIQUE_ID_BYTES = 128
@@ -157,6 +157,7 @@ def lib() -> C.CDLL:
     L.rlcu_zero1_create.argtypes = [vp, C.c_int, C.c_int, vp, vp, vp, u64, vp, vp, vp, u32, C.POINTER(vp)]
     L.rlcu_zero1_step.argtypes = [vp, vp, f, f, vp, vp, u32, u32, vp]
     L.rlcu_zero1_poll_error.argtypes = [vp]
+    L.rlcu_zero1_check.argtypes = [vp]
     L.rlcu_zero1_destroy.argtypes = [vp, C.c_int]
     L.rlcu_checkpoint_save.argtypes = [C.c_char_p, vp, vp, vp, vp, vp]
     L.rlcu_checkpoint_peek.argtypes = [C.c_char_p, vp]
@@ -324,6 +325,10 @@ class Zero1:
 
     def poll_error(self):
         check(lib().rlcu_zero1_poll_error(self.handle))
+
+    def check(self):
+        """Wait for the device and raise if a bounded wait of an exchange kernel gave up or NCCL failed."""
+        check(lib().rlcu_zero1_check(self.handle))
 
     def close(self, abort=False):
         if self.handle:

@@ -521,6 +521,13 @@ int rlcu_zero1_poll_error(rlcu_zero1* z) {
     return RLCU_OK;
 }
 
+int rlcu_zero1_check(rlcu_zero1* z) {
+    if (!z) return set_error(RLCU_ERR_INVALID, "null context");
+    const int rc = rlcu_tensor_list_check(z->list);      // waits for the device; a bounded wait that gave up
+    if (rc) return rc;
+    return rlcu_zero1_poll_error(z);
+}
+
 int rlcu_zero1_destroy(rlcu_zero1* z, int abort) {
     if (!z) return RLCU_OK;
     int rc = RLCU_OK;

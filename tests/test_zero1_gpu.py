@@ -69,7 +69,7 @@ def _run_rank(rank, world, uid, pkg, O, torch, use_master, mode=0, bf=False, ext
     hp = pkg.hparams(LR, B1, B2, EPS, T)
     z.step(hp, stat.data_ptr(), 1.0, MAX_NORM, None, pkg.STEP_ROUND_CLIP_FP16 | extra_flags)
     torch.cuda.synchronize()
-    z.poll_error()
+    z.check()
     out = dict(p=p_pool.cpu().numpy().view(np.uint16), g=g_pool.cpu().numpy().view(np.uint16),
                m=m_sh.cpu().numpy(), v=v_sh.cpu().numpy(), stat=stat.cpu().numpy(), lo=lo, S=S)
     if use_master:
