@@ -32,3 +32,21 @@ def test_reference_arm_other_ranks_stay_silent():
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2"],
                        capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0 and r.stdout.strip() == ""
+
+
+def test_pool_hash_sees_single_bit_and_order_changes():
+    """The hash the sharded arm all-reduces (MIN and MAX) to check that every rank holds the same
+    parameter pool: equal pools give equal hashes, one flipped bit or two swapped words do not."""
+    import torch
+    sys.path.insert(0, ROOT)
+    import bench
+    g = torch.Generator().manual_seed(0)
+    a = torch.randint(-30000, 30000, (1 << 18,), generator=g, dtype=torch.int16)
+    h = bench.pool_hash(torch, a)
+    assert torch.equal(h, bench.pool_hash(torch, a.clone()))
+    b = a.clone()
+    b[12345] ^= 1
+    assert not torch.equal(h, bench.pool_hash(torch, b))
+    c = a.clone().view(torch.int64)
+    c[[7, 9000]] = c[[9000, 7]]
+    assert not torch.equal(h, bench.pool_hash(torch, c.view(torch.int16)))
