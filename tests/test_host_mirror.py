@@ -17,6 +17,66 @@ REF = reference_checkout() or ""
 NVCC = ["nvcc", "-std=c++17", "-O2", "--expt-relaxed-constexpr", "-gencode", "arch=compute_100a,code=sm_100a"]
 
 
+def _third_party_shim(dest):
+    """RL.cu expects nlohmann/json and xxhash under third_party/ and does not vendor them; installed
+    copies of the same libraries are put on the include path through symlinks (nothing is copied)."""
+    import glob
+    import sysconfig
+    site = sysconfig.get_paths()["purelib"]
+    json_hpp = glob.glob(os.path.join(site, "include", "cudnn_frontend", "thirdparty", "nlohmann", "json.hpp"))
+    xxhash_h = glob.glob(os.path.join(site, "pyarrow", "include", "arrow", "vendored", "xxhash", "xxhash.h"))
+    if not json_hpp or not xxhash_h:
+        pytest.skip("nlohmann/json or xxhash, which RL.cu expects under third_party/, is not installed")
+    shim = dest / "third_party"
+    shim.mkdir(parents=True)
+    os.symlink(json_hpp[0], shim / "json.hpp")
+    os.symlink(xxhash_h[0], shim / "xxhash.h")
+    return str(dest)
+
+
+def _patched_training_headers(dest):
+    """A copy of RL.cu's include/training/ in which trainer.h and GRPO_trainer.h carry
+    include/training/trainer_fused_step.patch and optimizer.h is this repository's."""
+    tdir = dest / "include" / "training"
+    tdir.mkdir(parents=True)
+    ref_training = os.path.join(REF, "include", "training")
+    for name in os.listdir(ref_training):
+        if name in ("trainer.h", "GRPO_trainer.h"):
+            shutil.copy(os.path.join(ref_training, name), tdir / name)
+            os.chmod(tdir / name, 0o644)
+        elif name == "optimizer.h":
+            os.symlink(os.path.join(ROOT, "include", "training", "optimizer.h"), tdir / name)
+        else:
+            os.symlink(os.path.join(ref_training, name), tdir / name)
+    with open(os.path.join(ROOT, "include", "training", "trainer_fused_step.patch")) as patch:
+        subprocess.run(["patch", "-p1", "-d", str(dest)], stdin=patch, check=True)
+    return str(dest / "include")
+
+
+@pytest.fixture(scope="module")
+def reference_objects(tmp_path_factory):
+    """Every RL.cu source of its `kernels` and `model` libraries except src/kernels/adamw.cu
+    (CMakeLists.txt:58-79), compiled once for the link tests below."""
+    import glob
+    if not REF or shutil.which("nvcc") is None:
+        pytest.skip("no checkout of RL.cu here")
+    work = tmp_path_factory.mktemp("refobj")
+    shim = _third_party_shim(work / "shim")
+    sources = [s for pat in ("src/kernels/*.cu", "src/kernels/*.cpp", "src/model/*.cu")
+               for s in sorted(glob.glob(os.path.join(REF, pat))) if not s.endswith("kernels/adamw.cu")]
+    objs = []
+    procs = []
+    for src in sources:
+        obj = str(work / (os.path.basename(src) + ".o"))
+        objs.append(obj)
+        procs.append(subprocess.Popen(["nvcc", "-std=c++17", "-O0", "--expt-relaxed-constexpr", "-w", "-gencode",
+                                       "arch=compute_100a,code=sm_100a", "-I", os.path.join(REF, "include"), "-I", shim,
+                                       "-c", src, "-o", obj]))
+    for pr in procs:
+        assert pr.wait() == 0
+    return objs, shim
+
+
 @pytest.fixture(scope="module")
 def mirror_binary(pkg, tmp_path_factory):
     if shutil.which("nvcc") is None:
@@ -54,31 +114,17 @@ def test_mirror_program_passes_on_the_gpu(mirror_binary):
     assert "[FAIL]" not in r.stdout and r.stdout.count("[PASS]") >= 17
 
 
-def test_reference_test_binary_links_against_the_library(pkg, tmp_path):
+def test_reference_test_binary_links_against_the_library(pkg, tmp_path, reference_objects):
     """Link-level drop-in: RL.cu's tests/test_adamw.cu with RL.cu's own headers and every RL.cu
     source except src/kernels/adamw.cu links into an executable whose launch_adamw_fp16 /
     launch_adamw_fp32 come from librlcu_b200.so.  (Running it needs real Qwen3-0.6B weights, which
     are not here; it exits at once without them, tests/test_adamw.cu:507-510.)"""
-    import glob
-    import sysconfig
+    objs, shim = reference_objects
     src = os.path.join(REF, "tests", "test_adamw.cu")
-    if not os.path.exists(src) or shutil.which("nvcc") is None:
-        pytest.skip("no checkout of RL.cu here")
-    site = sysconfig.get_paths()["purelib"]
-    json_hpp = glob.glob(os.path.join(site, "include", "cudnn_frontend", "thirdparty", "nlohmann", "json.hpp"))
-    xxhash_h = glob.glob(os.path.join(site, "pyarrow", "include", "arrow", "vendored", "xxhash", "xxhash.h"))
-    if not json_hpp or not xxhash_h:
-        pytest.skip("nlohmann/json or xxhash, which RL.cu expects under third_party/, is not installed")
-    shim = tmp_path / "shim" / "third_party"
-    shim.mkdir(parents=True)
-    os.symlink(json_hpp[0], shim / "json.hpp")
-    os.symlink(xxhash_h[0], shim / "xxhash.h")
-    sources = [s for pat in ("src/kernels/*.cu", "src/kernels/*.cpp", "src/model/*.cu")
-               for s in sorted(glob.glob(os.path.join(REF, pat))) if not s.endswith("kernels/adamw.cu")]
     lib_dir = os.path.join(ROOT, "rl.cu_b200", "lib")
     exe = str(tmp_path / "test_adamw")
     cmd = ["nvcc", "-std=c++17", "-O0", "--expt-relaxed-constexpr", "-w", "-gencode", "arch=compute_100a,code=sm_100a",
-           "-I", os.path.join(REF, "include"), "-I", str(tmp_path / "shim"), src] + sources + \
+           "-I", os.path.join(REF, "include"), "-I", shim, src] + objs + \
           ["-o", exe, "-lcublas", "-L", lib_dir, "-lrlcu_b200", "-Xlinker", f"-rpath={lib_dir}"]
     subprocess.run(cmd, check=True)
     undefined = subprocess.run(["nm", "-D", "--undefined-only", exe], check=True, capture_output=True, text=True).stdout
@@ -89,6 +135,32 @@ def test_reference_test_binary_links_against_the_library(pkg, tmp_path):
 
 
 @pytest.mark.parametrize("program", ["train_sft", "train_grpo"])
+def test_reference_trainers_link_with_the_fused_step(pkg, tmp_path, reference_objects, program):
+    """The whole trainer binary: RL.cu's tests/train_sft.cu / tests/train_grpo.cu, compiled against
+    the patched trainer headers and this repository's optimizer.h, link with RL.cu's own model and
+    kernel objects (without src/kernels/adamw.cu) and librlcu_b200.so; the executable takes the
+    statistics pass and the multi-tensor update from the shared library and no longer needs
+    RL.cu's launch_adamw_* at all."""
+    if shutil.which("patch") is None:
+        pytest.skip("patch is not installed")
+    objs, shim = reference_objects
+    src = os.path.join(REF, "tests", f"{program}.cu")
+    patched = _patched_training_headers(tmp_path / "patched")
+    lib_dir = os.path.join(ROOT, "rl.cu_b200", "lib")
+    exe = str(tmp_path / program)
+    cmd = ["nvcc", "-std=c++17", "-O0", "--expt-relaxed-constexpr", "-w", "-gencode", "arch=compute_100a,code=sm_100a",
+           "-I", os.path.join(ROOT, "include"), "-I", patched, "-I", os.path.join(REF, "include"), "-I", shim, src] + objs + \
+          ["-o", exe, "-lcublas", "-L", lib_dir, "-lrlcu_b200", "-Xlinker", f"-rpath={lib_dir}"]
+    subprocess.run(cmd, check=True)
+    undefined = subprocess.run(["nm", "-D", "--undefined-only", exe], check=True, capture_output=True, text=True).stdout
+    for sym in ("rlcu_gradstat", "rlcu_adamw_multi_step", "rlcu_tensor_list_create", "rlcu_half_to_float"):
+        assert sym in undefined, f"{sym} is not taken from the shared library"
+    for sym in pkg.CXX_EXPORTS:
+        assert sym not in undefined, "the patched trainer still calls RL.cu's launchers"
+    assert "librlcu_b200.so" in subprocess.run(["ldd", exe], check=True, capture_output=True, text=True).stdout
+
+
+@pytest.mark.parametrize("program", ["train_sft", "train_grpo"])
 def test_reference_trainers_compile_with_the_fused_step_patch(tmp_path, program):
     """The trainer side of the drop-in: include/training/trainer_fused_step.patch, applied to
     copies of RL.cu's trainer.h and GRPO_trainer.h, replaces clip_grad_norm_ + optimizer_.step
@@ -96,38 +168,15 @@ def test_reference_trainers_compile_with_the_fused_step_patch(tmp_path, program)
     by AdamWOptimizer::clip_and_step of this repository's optimizer.h.  RL.cu's own
     tests/train_sft.cu and tests/train_grpo.cu then compile, call the fused library entry
     points, and no longer contain RL.cu's sum-of-squares and scale kernels."""
-    import glob
-    import sysconfig
     src = os.path.join(REF, "tests", f"{program}.cu")
     if not os.path.exists(src) or shutil.which("nvcc") is None or shutil.which("patch") is None:
         pytest.skip("no checkout of RL.cu here")
-    site = sysconfig.get_paths()["purelib"]
-    json_hpp = glob.glob(os.path.join(site, "include", "cudnn_frontend", "thirdparty", "nlohmann", "json.hpp"))
-    xxhash_h = glob.glob(os.path.join(site, "pyarrow", "include", "arrow", "vendored", "xxhash", "xxhash.h"))
-    if not json_hpp or not xxhash_h:
-        pytest.skip("nlohmann/json or xxhash, which RL.cu expects under third_party/, is not installed")
-    shim = tmp_path / "shim" / "third_party"
-    shim.mkdir(parents=True)
-    os.symlink(json_hpp[0], shim / "json.hpp")
-    os.symlink(xxhash_h[0], shim / "xxhash.h")
-    # a training/ directory that is RL.cu's, with the two patched headers and this repository's optimizer.h
-    tdir = tmp_path / "patched" / "include" / "training"
-    tdir.mkdir(parents=True)
-    ref_training = os.path.join(REF, "include", "training")
-    for name in os.listdir(ref_training):
-        if name in ("trainer.h", "GRPO_trainer.h"):
-            shutil.copy(os.path.join(ref_training, name), tdir / name)
-            os.chmod(tdir / name, 0o644)
-        elif name == "optimizer.h":
-            os.symlink(os.path.join(ROOT, "include", "training", "optimizer.h"), tdir / name)
-        else:
-            os.symlink(os.path.join(ref_training, name), tdir / name)
-    with open(os.path.join(ROOT, "include", "training", "trainer_fused_step.patch")) as patch:
-        subprocess.run(["patch", "-p1", "-d", str(tmp_path / "patched")], stdin=patch, check=True)
+    shim = _third_party_shim(tmp_path / "shim")
+    patched = _patched_training_headers(tmp_path / "patched")
     obj = str(tmp_path / f"{program}.o")
     cmd = ["nvcc", "-std=c++17", "-O0", "--expt-relaxed-constexpr", "-w", "-gencode", "arch=compute_100a,code=sm_100a",
-           "-I", os.path.join(ROOT, "include"), "-I", str(tmp_path / "patched" / "include"),
-           "-I", os.path.join(REF, "include"), "-I", str(tmp_path / "shim"), "-c", src, "-o", obj]
+           "-I", os.path.join(ROOT, "include"), "-I", patched,
+           "-I", os.path.join(REF, "include"), "-I", shim, "-c", src, "-o", obj]
     subprocess.run(cmd, check=True)
     syms = subprocess.run(["nm", "-C", obj], check=True, capture_output=True, text=True).stdout
     for wanted in ("U rlcu_gradstat", "U rlcu_adamw_multi_step", "clip_and_step"):
