@@ -85,9 +85,10 @@ enum {
                                        (cp.async.bulk through shared-memory stages) instead of
                                        per-thread loads and stores; same results.  Without this
                                        flag or the next the library picks: lists that are mostly
-                                       FP16 weights with FP32 masters (28 bytes per element in
-                                       eight streams) take the bulk-copy kernel, which is about
-                                       5 % faster there; all others the direct kernel.       */
+                                       FP16 weights with FP32 masters or with FP32 gradients (24
+                                       to 30 bytes per element in eight or more streams) take the
+                                       bulk-copy kernel, which is 5-7 % faster there; all others
+                                       the direct kernel.                                     */
     RLCU_STEP_DIRECT = 16u          /* force the per-thread load/store kernel                 */
 };
 
